@@ -8,7 +8,9 @@ from .registry import (architecture_entry, load_config, model_type_of, parse_con
 from .families import DecoderDraft, parse_qwen3, parse_rope_scaling
 from .madevik import parse_madevik
 from .movivik import parse_movivik
+from .bozevik import parse_bozevik
 
 register_architecture("qwen3", parse_qwen3, replace=True)
 register_architecture("Madevik", parse_madevik, replace=True)
 register_architecture("Movivik", parse_movivik, replace=True)
+register_architecture("Bozevik", parse_bozevik, replace=True)

@@ -57,7 +57,8 @@ class RopeTableSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str = "rmsnorm"                  # rmsnorm | dynamic_tanh (tanh(a x) * w + b: no statistics, eps unused)
+    kind: str = "rmsnorm"                  # rmsnorm | dynamic_tanh (tanh(a x) * w + b: no statistics, eps unused) |
+                                           # layernorm ((x - mean) / sqrt(variance + eps) * w, no bias)
     eps: float = 1e-6
     gain_name: str = "weight"              # rmsnorm: the gain is the tensor <the norm's name> + gain_name ("": the name itself)
 
@@ -209,8 +210,13 @@ class ParallelMixersSpec(MixerSpec):
 @dataclass(frozen=True)
 class LatentAttentionSpec(MixerSpec):
     """Causal softmax attention whose keys and values are two projections of one cached latent row per position
-    (c_t = rmsnorm(Wd h_t) * gain, k = Wuk c, v = Wuv c per head), without rotation, with a sigmoid gate per head on the
-    output (`gated`)."""
+    (c_t = rmsnorm(Wd h_t) * gain, k = Wuk c, v = Wuv c per head), with a sigmoid gate per head on the output (`gated`).
+
+    Beyond that form: queries that go through a latent of their own (`query_rank` > 0: q = Wuq (rmsnorm(Wdq h) * gain));
+    a rotated key part of `rope_dim` values that all heads share, cached beside the latent (the down projection then has
+    rank + rope_dim rows, the last rope_dim are not normed; a query head is [key_dim values, then rope_dim rotated values]
+    and its score is the sum of both dot products); and a run that makes no latent of its own but reads the rows another
+    run cached (`own_latent` False: no down projection; the schedule's `cache_of` names the run)."""
     kind: str = field(default="latent_attention", init=False)
     heads: int = 0
     key_dim: int = 0
@@ -220,11 +226,24 @@ class LatentAttentionSpec(MixerSpec):
     norm_eps: float = 1e-6
     window: int = 0
     gated: bool = True
+    query_rank: int = 0                    # 0: q = Wq h; else the width of the queries' latent
+    rope_dim: int = 0                      # 0: nothing rotates; else the width of the shared rotated key part
+    rope_table: int = -1                   # index into Decoder.rope_tables (its rotary_dim <= rope_dim values are rotated)
+    own_latent: bool = True                # False: the run reads another run's cached rows and has no down projection
 
     def __post_init__(self):
         for name in ("heads", "key_dim", "value_dim", "rank"):
             if getattr(self, name) <= 0:
                 raise ConfigError(f"latent attention: {name}={getattr(self, name)} must be positive")
+        if self.query_rank < 0 or self.rope_dim < 0:
+            raise ConfigError(f"latent attention: q_rank={self.query_rank} and rot_dim={self.rope_dim} must not be negative")
+        if (self.rope_dim > 0) != (self.rope_table >= 0):
+            raise ConfigError("latent attention: a rotated key part needs a rotary table, and a table a rotated part")
+
+    @property
+    def cache_dim(self) -> int:
+        """Values of a cached row: the latent and, behind it, the rotated key part."""
+        return self.rank + self.rope_dim
 
 
 @dataclass(frozen=True)
@@ -237,21 +256,26 @@ class DenseGluSpec(FeedForwardSpec):
     """down(act(gate x) * (up x)) (Mlp.java:21)."""
     kind: str = field(default="dense_glu", init=False)
     hidden: int = 0
-    activation: str = "silu"               # silu | gelu_tanh (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))))
+    activation: str = "silu"               # silu | gelu_tanh (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) |
+                                           # swish_clamped: g sigmoid(1.702 g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit)
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")   # gate, up, down
+    limit: float = 0.0                     # swish_clamped: where gate and up are cut off
 
     def __post_init__(self):
         if self.hidden <= 0:
             raise ConfigError(f"intermediate_size must be positive for a dense feed-forward, got {self.hidden}")
-        if self.activation not in ("silu", "gelu_tanh"):
-            raise ConfigError(f"unsupported hidden_act {self.activation!r}: silu (SwiGLU) and gelu_tanh are built")
+        if self.activation not in ("silu", "gelu_tanh", "swish_clamped"):
+            raise ConfigError(f"unsupported hidden_act {self.activation!r}: silu (SwiGLU), gelu_tanh and swish_clamped are built")
+        if self.activation == "swish_clamped" and not self.limit > 0:
+            raise ConfigError(f"feed-forward: limit={self.limit} must be positive")
 
 
 @dataclass(frozen=True)
 class RoutedExpertsSpec(FeedForwardSpec):
     """`experts` gated feed-forwards of `hidden` units, of which a token uses `top`: scores s = sigmoid(Wr h); the `top`
     largest of s + correction are chosen (if `correction`); the weights are the chosen s over their sum (+ 1e-20, if
-    `normalize`), times `scale`."""
+    `normalize`), times `scale`. `weight_on` "output": y = sum_e w_e expert_e(h); "input": y = sum_e expert_e(w_e h).
+    `shared`: a dense gated feed-forward (tensors under `shared.`) that every token runs, added to the experts' sum."""
     kind: str = field(default="routed_experts", init=False)
     experts: int = 0
     top: int = 0
@@ -259,15 +283,24 @@ class RoutedExpertsSpec(FeedForwardSpec):
     scale: float = 1.0
     correction: bool = True
     normalize: bool = True
-    activation: str = "silu"
+    activation: str = "silu"               # silu | swish_clamped (with `limit`; see DenseGluSpec)
+    limit: float = 0.0
+    weight_on: str = "output"              # output | input
+    shared: Optional["DenseGluSpec"] = None
 
     def __post_init__(self):
         if self.experts <= 0 or self.hidden <= 0:
             raise ConfigError(f"routed experts: experts={self.experts} and ff={self.hidden} must be positive")
         if not 1 <= self.top <= self.experts:
             raise ConfigError(f"routed experts: top={self.top} must lie in [1, experts={self.experts}]")
-        if self.activation != "silu":
-            raise ConfigError(f"unsupported expert activation {self.activation!r}: only silu is built")
+        if self.activation not in ("silu", "swish_clamped"):
+            raise ConfigError(f"unsupported expert activation {self.activation!r}: silu and swish_clamped are built")
+        if self.activation == "swish_clamped" and not self.limit > 0:
+            raise ConfigError(f"routed experts: limit={self.limit} must be positive")
+        if self.weight_on not in ("output", "input"):
+            raise ConfigError(f"routed experts: weight_on={self.weight_on!r} (built: output, input)")
+        if self.weight_on == "input" and self.activation == "silu":
+            raise ConfigError("routed experts: a weight on the expert's input is built for swish_clamped experts")
 
 
 @dataclass(frozen=True)
@@ -299,9 +332,12 @@ class LayerSpec:
     norm: NormSpec
     arrangement: str = "pre_norm"          # x += s * mixer(norm(x)); x += s * ffn(norm(x)), s = residual_scale
                                            # sandwich_norm: x += post(mixer(norm(x))); x += post'(ffn(norm'(x)))
+                                           # post_norm: x += norm(mixer(x)); x += norm'(ffn(x)): the parts read x itself
     names: LayerNames = LayerNames()
     residual_scale: float = 1.0
     prefix: Optional[str] = None           # the layer's checkpoint prefix where it is not ModelNames.layer.format(index)
+    token_shift: str = ""                  # "": none; else the name (under the layer's prefix) of a vector mu: the mixer
+                                           # reads x_t + (x_(t-1) - x_t) * mu, x_(-1) = 0 (`post_norm` arrangement)
 
 
 @dataclass(frozen=True)
@@ -326,6 +362,7 @@ class Core:
     eos: Tuple[int, ...]
     max_positions: int
     description: str = ""
+    logit_scale: float = 1.0               # the head's result is multiplied by it
 
 
 @dataclass(frozen=True)
@@ -336,6 +373,9 @@ class Decoder:
     final_norm: NormSpec
     schedule: Tuple[LayerRun, ...] = ()
     names: ModelNames = ModelNames()
+    depth_mix: str = ""                    # "": a run hands its result on as it is; else the name (under each run's layer
+                                           # prefix) of a vector a of i + 2 weights for run i: what goes on is the sum over
+                                           # j <= i + 1 of a[j] X_j, X_0 the embedded rows, X_(j+1) the result of run j
 
     def __post_init__(self):
         if len(self.layers) != self.core.layers or self.core.layers <= 0:
@@ -362,4 +402,4 @@ class Decoder:
 
     def with_schedule(self, schedule) -> "Decoder":
         runs = tuple(r if isinstance(r, LayerRun) else LayerRun(*r) for r in schedule)
-        return Decoder(self.core, self.layers, self.rope_tables, self.final_norm, runs, self.names)
+        return Decoder(self.core, self.layers, self.rope_tables, self.final_norm, runs, self.names, self.depth_mix)

@@ -164,6 +164,23 @@ __device__ __forceinline__ float glu_act(float z, int kind) {
     return z / (1.f + expf(-t));
 }
 
+// The gated unit of a feed-forward from its two inputs. `word` is the products' `swiglu` argument: the activation's number
+// (act(gate) * up), or, for the clamped unit, 3 in its two lowest bits and the float32 bits of the limit above them (the
+// limit's own two lowest bits dropped): g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+enum : int { GLU_SWISH_CLAMPED = 3 };
+constexpr float kSwishAlpha = 1.702f;
+template <bool FAST>
+__device__ __forceinline__ float glu_unit(float gate, float up, int word) {
+    if ((word & 3) == GLU_SWISH_CLAMPED) {
+        const float limit = __int_as_float(word & ~3);
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        const float t = kSwishAlpha * g;
+        if constexpr (FAST) return __fdividef(g, 1.f + __expf(-t)) * (u + 1.f);
+        return __fmul_rn(g / (1.f + expf(-t)), u + 1.f);
+    }
+    return __fmul_rn(glu_act<FAST>(gate, word), up);
+}
+
 // A vector (gain, bias) whose stored type is known only at run time.
 struct VecRef {
     const void* p;

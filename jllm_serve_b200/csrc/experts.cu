@@ -109,7 +109,45 @@ __global__ void scale_expert_hidden_vec_kernel(T* __restrict__ hidden, const flo
     }
 }
 
+// The gated unit whose two inputs are cut off: g = min(w gate, limit), u = clamp(w up, -limit, limit), y = g sigmoid(alpha g)
+// (u + 1); w the row's weight for the expert the unit belongs to (the weight multiplies the expert's INPUT, which by
+// linearity of the two products is the same as multiplying their results), 1 without a weight table. gate_up [rows,
+// 2 * experts * ff]: all gate values, then all up values. An expert the row does not use (w = 0) gives exact zeros.
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights, T* __restrict__ out,
+                                   int experts, int ff, float limit, float alpha, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t width = (size_t)experts * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width, col = i - r * width;
+        const float w = weights ? weights[r * experts + col / ff] : 1.f;
+        const T* row = gate_up + r * 2 * width;
+        const float g = fminf(__fmul_rn(w, to_float(row[col])), limit);
+        const float u = fminf(fmaxf(__fmul_rn(w, to_float(row[width + col])), -limit), limit);
+        out[i] = from_float<T>(__fmul_rn(g / (1.f + expf(-__fmul_rn(alpha, g))), u + 1.f));
+    }
+}
+
 }  // namespace
+
+// gate_up [rows, 2 * experts * ff], out [rows, experts * ff], both contiguous and of type `dtype`; weights [rows, experts]
+// float32 or null.
+JLLM_EXPORT int jllm_glu_clamped(const void* gate_up, const float* weights, void* out, int dtype, int rows, int experts, int ff,
+                                 float limit, float alpha, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0 && limit > 0.f, "glu_clamped: rows=%d experts=%d ff=%d limit=%g", rows,
+                 experts, ff, (double)limit);
+    if (rows == 0) return JLLM_OK;
+    const size_t total = (size_t)rows * experts * ff;
+    const int blocks = (int)min((size_t)65535, (total + 255) / 256);
+    if (dtype == JLLM_F32)
+        jllm_launch(glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)gate_up, weights,
+                    (float*)out, experts, ff, limit, alpha, total);
+    else
+        jllm_launch(glu_clamped_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                    (const __nv_bfloat16*)gate_up, weights, (__nv_bfloat16*)out, experts, ff, limit, alpha, total);
+    return jllm_check_launch("glu_clamped");
+}
 
 // h [rows, ld] of type `dtype` (the normed rows); router [experts, dim] float32; correction [experts] or null;
 // weights [rows, experts] float32.

@@ -115,7 +115,7 @@ struct TileEpilogue {
             for (int j = 0; j < 16; ++j) {
                 const int cg = (j >> 3) * 16 + (j & 7);
                 const float gt = __uint_as_float(v[cg]), up = __uint_as_float(v[cg + 8]);
-                hv[j] = glu_act<true>(gt, swiglu) * up;
+                hv[j] = glu_unit<true>(gt, up, swiglu);
             }
             if (sizeof(Tout) == 2 && n_base + 32 <= N && ((((uintptr_t)dst) & 15u) == 0)) {
                 uint32_t p[8];

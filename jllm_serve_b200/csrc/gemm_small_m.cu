@@ -168,7 +168,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
             float u = 0.f;
 #pragma unroll
             for (int wi = 0; wi < WARPS; ++wi) u += red[(size_t)wi * ROWS * TOK + e + 8];
-            out[(size_t)tok * ldo + (n >> 4) * 8 + (row & 7)] = from_float<Tout>(__fmul_rn(glu_act<false>(v, swiglu), u));
+            out[(size_t)tok * ldo + (n >> 4) * 8 + (row & 7)] = from_float<Tout>(glu_unit<false>(v, u, swiglu));
             continue;
         }
         if (has_bias) v += bias[n];

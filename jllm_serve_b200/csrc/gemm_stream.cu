@@ -185,7 +185,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                         const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
                         if ((lane & 8) == 0 && n + 8 < N && m0 + j < M) {
                             const float gt = v[j];
-                            out[(size_t)(m0 + j) * ldo + unit] = from_float<Tout>(glu_act<true>(gt, swiglu) * other);
+                            out[(size_t)(m0 + j) * ldo + unit] = from_float<Tout>(glu_unit<true>(gt, other, swiglu));
                         }
                     }
                 } else if (n < N) {

@@ -7,6 +7,12 @@
 // (kv_heads = 1, head_dim = rank). Here:
 //
 //   latent_norm_store   RMSNorm of the down-projected rows (float32 arithmetic) and their write into the paged cache
+//   latent_prepare      the same for a mixer whose queries go through a latent of their own and whose cached row ends in a
+//                       rotated key part that all heads share: from one float32 row of the stacked down projections it
+//                       makes the normed query latent (compute type) and the cached row [normed latent, rotated part]
+//   rope_heads          the rotated part of every query head, turned by the row's position and placed behind the head's
+//                       latent-space query (where `gemm_heads` put it), so that one dot product with a cached row gives
+//                       both terms of the score
 //   gemm_heads          out[r, h, :] = f(r, h) * W[h] a[r, h, :] for every head h at once (W [heads, N, K]); f = alpha, or
 //                       alpha * sigmoid(gate[r, h]) (the mixer's output gate). float32: on the CUDA cores with one
 //                       accumulator per element in ascending k. bfloat16: 64 x 64 tiles per (head, block) on the tensor
@@ -39,12 +45,90 @@ latent_norm_store_kernel(const T* __restrict__ src, int ld, VecRef gain, const i
         dst[i] = from_float<T>(__fmul_rn(__fmul_rn(to_float(row[i]), inv), gain[i]));
 }
 
+// Turns neighbouring pairs: (u, v) -> (u cos - v sin, v cos + u sin), the angle of pair i from the position's table row.
+__device__ __forceinline__ void turn_pair(float u, float v, float c, float s, float& a, float& b) {
+    a = __fsub_rn(__fmul_rn(u, c), __fmul_rn(v, s));
+    b = __fadd_rn(__fmul_rn(v, c), __fmul_rn(u, s));
+}
+
+// One block per row. src [rows, ld] float32: the query latent's q_rank values at q_off (q_rank = 0: none), the latent's
+// rank values at d_off and the rope_dim values of the rotated part behind them. cq [rows, q_rank]; cache rows of
+// rank + rope_dim values. cos / sin [positions, rotary_dim / 2]: pairs (2i, 2i + 1), i < rotary_dim / 2, of the rotated
+// part are turned, the rest of it is copied.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prepare_kernel(const float* __restrict__ src, int ld, int q_off, int q_rank, VecRef q_gain, T* __restrict__ cq, int d_off,
+                      int rank, int rope_dim, VecRef gain, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                      int rotary_dim, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ cache,
+                      float eps, long long cache_rows, int write_latent) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const float* row = src + (size_t)r * ld;
+    if (q_rank > 0) {
+        const float* q = row + q_off;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss = fmaf(q[i], q[i], ss);
+        ss = block_sum(ss, scratch);
+        const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+        T* dst = cq + (size_t)r * q_rank;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) dst[i] = from_float<T>(__fmul_rn(__fmul_rn(q[i], inv), q_gain[i]));
+    }
+    if (!write_latent) return;
+    const float* d = row + d_off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(d[i], d[i], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)rank + eps);
+    const int slot = slots[r];
+    if (!jllm_in_bounds(slot, cache_rows, BOUNDS_SLOT)) return;
+    T* dst = cache + (size_t)slot * (rank + rope_dim);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_float<T>(__fmul_rn(__fmul_rn(d[i], inv), gain[i]));
+    const int half = rotary_dim / 2;
+    const float* c = cos_t + (size_t)positions[r] * half;
+    const float* s = sin_t + (size_t)positions[r] * half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float a, b;
+        turn_pair(d[rank + 2 * i], d[rank + 2 * i + 1], c[i], s[i], a, b);
+        dst[rank + 2 * i] = from_float<T>(a);
+        dst[rank + 2 * i + 1] = from_float<T>(b);
+    }
+    for (int i = rotary_dim + threadIdx.x; i < rope_dim; i += blockDim.x) dst[rank + i] = from_float<T>(d[rank + i]);
+}
+
+// q [rows, ldq]: head h's rope_dim values at h * q_head + q_off; out [rows, ldo]: they go to h * o_head + o_off.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_heads_kernel(const T* __restrict__ q, int ldq, int q_head, int q_off, T* __restrict__ out, int ldo, int o_head, int o_off,
+                  int heads, int rope_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotary_dim,
+                  const int* __restrict__ positions) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, half = rotary_dim / 2, pairs = rope_dim / 2;
+    const float* c = cos_t + (size_t)positions[r] * half;
+    const float* s = sin_t + (size_t)positions[r] * half;
+    for (int e = threadIdx.x; e < heads * pairs; e += blockDim.x) {
+        const int h = e / pairs, i = e - h * pairs;
+        const T* src = q + (size_t)r * ldq + (size_t)h * q_head + q_off + 2 * i;
+        T* dst = out + (size_t)r * ldo + (size_t)h * o_head + o_off + 2 * i;
+        float a = to_float(src[0]), b = to_float(src[1]);
+        if (i < half) turn_pair(a, b, c[i], s[i], a, b);
+        dst[0] = from_float<T>(a);
+        dst[1] = from_float<T>(b);
+    }
+    if (rope_dim & 1) {        // an odd width's last value is never part of a pair
+        for (int h = threadIdx.x; h < heads; h += blockDim.x)
+            out[(size_t)r * ldo + (size_t)h * o_head + o_off + rope_dim - 1] = q[(size_t)r * ldq + (size_t)h * q_head + q_off + rope_dim - 1];
+    }
+}
+
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_heads_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, T* __restrict__ out, int ldo,
-                  const T* __restrict__ gate, int ld_gate, float alpha, int M, int N, int K) {
+                  const T* __restrict__ gate, int ld_gate, float alpha, int M, int N, int K, int a_head, int o_head) {
     __shared__ float as[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     pdl_wait();
@@ -52,7 +136,7 @@ gemm_heads_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, T* 
     const int tid = threadIdx.x, h = blockIdx.z;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;
-    const T* ah = a + (size_t)h * K;
+    const T* ah = a + (size_t)h * a_head;
     const T* wh = w + (size_t)h * N * K;
     float acc[TM][TN] = {};
     const int lr = tid / 4, lk = (tid % 4) * 4;
@@ -91,7 +175,7 @@ gemm_heads_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, T* 
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int n = n0 + tx * TN + j;
-            if (n < N) out[(size_t)m * ldo + (size_t)h * N + n] = from_float<T>(__fmul_rn(acc[i][j], f));
+            if (n < N) out[(size_t)m * ldo + (size_t)h * o_head + n] = from_float<T>(__fmul_rn(acc[i][j], f));
         }
     }
 }
@@ -112,14 +196,14 @@ template <bool VEC>
 __global__ void __launch_bounds__(128)
 gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
                       __nv_bfloat16* __restrict__ out, int ldo, const __nv_bfloat16* __restrict__ gate, int ld_gate,
-                      float alpha, int M, int N, int K) {
+                      float alpha, int M, int N, int K, int a_head, int o_head) {
     __shared__ __align__(16) __nv_bfloat16 as[64][HPAD];
     __shared__ __align__(16) __nv_bfloat16 ws[64][HPAD];
     pdl_wait();
     pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, h = blockIdx.z;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    const __nv_bfloat16* ah = a + (size_t)h * K;
+    const __nv_bfloat16* ah = a + (size_t)h * a_head;
     const __nv_bfloat16* wh = w + (size_t)h * N * K;
     float acc[8][4] = {};
     const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
@@ -170,7 +254,7 @@ gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_b
             const float gv = to_float(gate[(size_t)m * ld_gate + h]);
             f = __fmul_rn(alpha, 1.f / (1.f + expf(-gv)));
         }
-        __nv_bfloat16* dst = out + (size_t)m * ldo + (size_t)h * N;
+        __nv_bfloat16* dst = out + (size_t)m * ldo + (size_t)h * o_head;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int n = n0 + 8 * j + 2 * t;
@@ -201,27 +285,69 @@ JLLM_EXPORT int jllm_latent_norm_store(const void* src, int dtype, int ld, const
     return jllm_check_launch("latent_norm_store");
 }
 
-// a [M, lda] with head h's K values at column h * K; w [heads, N, K]; out [M, ldo] with head h's N values at h * N;
-// gate (or null) [M, ld_gate] with head h's gate at column h.
+// a [M, lda] with head h's K values at column h * a_head (0: h * K); w [heads, N, K]; out [M, ldo] with head h's N values at
+// h * o_head (0: h * N); gate (or null) [M, ld_gate] with head h's gate at column h.
 JLLM_EXPORT int jllm_gemm_heads(const void* a, int dtype, int lda, const void* w, void* out, int ldo, const void* gate,
-                                int ld_gate, float alpha, int M, int heads, int N, int K, cudaStream_t stream) {
+                                int ld_gate, float alpha, int M, int heads, int N, int K, int a_head, int o_head,
+                                cudaStream_t stream) {
     JLLM_REQUIRE(M >= 0 && heads > 0 && N > 0 && K > 0, "gemm_heads: M=%d heads=%d N=%d K=%d", M, heads, N, K);
-    JLLM_REQUIRE(lda >= heads * K && ldo >= heads * N && heads <= 65535 && (M + BM - 1) / BM <= 65535,
-                 "gemm_heads: lda=%d ldo=%d for %d heads of K=%d, N=%d", lda, ldo, heads, K, N);
+    if (a_head == 0) a_head = K;
+    if (o_head == 0) o_head = N;
+    JLLM_REQUIRE(a_head >= K && o_head >= N && lda >= (heads - 1) * a_head + K && ldo >= (heads - 1) * o_head + N &&
+                     heads <= 65535 && (M + BM - 1) / BM <= 65535,
+                 "gemm_heads: lda=%d ldo=%d for %d heads of K=%d (every %d), N=%d (every %d)", lda, ldo, heads, K, a_head, N, o_head);
     if (M == 0) return JLLM_OK;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
     static_assert(BM == 64 && BN == 64, "both kernels take 64 x 64 tiles");
     if (dtype == JLLM_F32) {
         jllm_launch(gemm_heads_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)a, lda,
-                    (const float*)w, (float*)out, ldo, (const float*)gate, ld_gate, alpha, M, N, K);
+                    (const float*)w, (float*)out, ldo, (const float*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
         return jllm_check_launch("gemm_heads");
     }
-    const bool vec = K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    const bool vec = K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
     if (vec)
         jllm_launch(gemm_heads_mma_kernel<true>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K);
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
     else
         jllm_launch(gemm_heads_mma_kernel<false>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K);
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
     return jllm_check_launch("gemm_heads");
+}
+
+// src [rows, ld] float32 (the stacked down projections); cq [rows, q_rank] and the cache [cache_rows, rank + rope_dim] of
+// type `dtype`. q_rank = 0: no query latent; write_latent = 0: the run caches nothing of its own.
+JLLM_EXPORT int jllm_latent_prepare(const float* src, int ld, int q_off, int q_rank, const void* q_gain, void* cq, int d_off,
+                                    int rank, int rope_dim, const void* gain, int gain_dtype, const float* cos_t,
+                                    const float* sin_t, int rotary_dim, const int* positions, const int* slots, void* cache,
+                                    int dtype, long long cache_rows, int rows, float eps, int write_latent, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && q_rank >= 0 && rank > 0 && rope_dim >= 0 && rotary_dim >= 0 && rotary_dim <= rope_dim &&
+                     rotary_dim % 2 == 0,
+                 "latent_prepare: rows=%d q_rank=%d rank=%d rope_dim=%d rotary_dim=%d", rows, q_rank, rank, rope_dim, rotary_dim);
+    if (rows == 0 || (q_rank == 0 && !write_latent)) return JLLM_OK;
+    const VecRef g{gain, gain_dtype}, qg{q_gain, gain_dtype};
+    if (dtype == JLLM_F32)
+        jllm_launch(latent_prepare_kernel<float>, dim3(rows), dim3(128), 0, stream, LAUNCH_DEPENDENT, src, ld, q_off, q_rank, qg,
+                    (float*)cq, d_off, rank, rope_dim, g, cos_t, sin_t, rotary_dim, positions, slots, (float*)cache, eps,
+                    cache_rows, write_latent);
+    else
+        jllm_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, LAUNCH_DEPENDENT, src, ld, q_off,
+                    q_rank, qg, (__nv_bfloat16*)cq, d_off, rank, rope_dim, g, cos_t, sin_t, rotary_dim, positions, slots,
+                    (__nv_bfloat16*)cache, eps, cache_rows, write_latent);
+    return jllm_check_launch("latent_prepare");
+}
+
+JLLM_EXPORT int jllm_rope_heads(const void* q, int dtype, int ldq, int q_head, int q_off, void* out, int ldo, int o_head,
+                                int o_off, int rows, int heads, int rope_dim, const float* cos_t, const float* sin_t,
+                                int rotary_dim, const int* positions, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && heads > 0 && rope_dim > 0 && rotary_dim >= 0 && rotary_dim <= rope_dim && rotary_dim % 2 == 0,
+                 "rope_heads: rows=%d heads=%d rope_dim=%d rotary_dim=%d", rows, heads, rope_dim, rotary_dim);
+    if (rows == 0) return JLLM_OK;
+    if (dtype == JLLM_F32)
+        jllm_launch(rope_heads_kernel<float>, dim3(rows), dim3(128), 0, stream, LAUNCH_DEPENDENT, (const float*)q, ldq, q_head,
+                    q_off, (float*)out, ldo, o_head, o_off, heads, rope_dim, cos_t, sin_t, rotary_dim, positions);
+    else
+        jllm_launch(rope_heads_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)q,
+                    ldq, q_head, q_off, (__nv_bfloat16*)out, ldo, o_head, o_off, heads, rope_dim, cos_t, sin_t, rotary_dim,
+                    positions);
+    return jllm_check_launch("rope_heads");
 }

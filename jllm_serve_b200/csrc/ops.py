@@ -165,7 +165,16 @@ class _Signatures:
     jllm_norm_sum = [P, P, P, P, P, I, I, I, F, F, I, P]
     jllm_norm_chain = [P, P, P, P, P, F, P, P, P, I, I, I, I, F, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
-    jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
+    jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, I, I, P]
+    jllm_latent_prepare = [P, I, I, I, P, P, I, I, I, P, I, P, P, I, P, P, P, I, ctypes.c_longlong, I, F, I, P]
+    jllm_rope_heads = [P, I, I, I, I, P, I, I, I, I, I, I, P, P, I, P, P]
+    jllm_glu_clamped = [P, P, P, I, I, I, I, F, F, P]
+    jllm_bounds_error_residual_paths = [P]
+    jllm_layernorm = [P, P, I, P, I, P, I, I, F, I, F, P]
+    jllm_norm_add = [P, P, P, I, P, I, I, I, F, I, P]
+    jllm_token_shift = [P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, P]
+    jllm_depth_mix = [P, ctypes.c_longlong, P, I, I, P, ctypes.c_longlong, P]
+    jllm_scale_values = [P, F, ctypes.c_longlong, P]
     jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
     jllm_scale_expert_hidden = [P, I, P, I, I, I, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
@@ -284,14 +293,105 @@ def latent_norm_store(src, gain, eps, slots, cache) -> None:
           slots.data_ptr(), cache.data_ptr(), cache.numel() // rank, src.shape[0], rank, float(eps), _stream())
 
 
-def gemm_heads(a, w, out, gate=None, alpha: float = 1.0) -> None:
+def gemm_heads(a, w, out, gate=None, alpha: float = 1.0, a_head: int = 0, out_head: int = 0) -> None:
     """out[r, h, :] = f * w[h] @ a[r, h, :] for all heads at once; a [rows, heads x K] (any row stride), w [heads, N, K]
-    contiguous, out [rows, heads x N]; f = alpha, or alpha * sigmoid(gate[r, h]) with gate a view [rows, heads]."""
+    contiguous, out [rows, heads x N]; f = alpha, or alpha * sigmoid(gate[r, h]) with gate a view [rows, heads]. `a_head` /
+    `out_head`: the distance between the heads of a row where it is more than K / N (a head's values are then the first K of
+    every a_head values of a, and go to the first N of every out_head values of out)."""
     heads, N, K = w.shape
     assert a.dtype == w.dtype == out.dtype and w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
-    assert a.shape[1] == heads * K and out.shape[1] == heads * N and (gate is None or gate.dtype == a.dtype)
+    assert a.shape[1] >= (heads - 1) * (a_head or K) + K and out.shape[1] >= (heads - 1) * (out_head or N) + N
+    assert gate is None or gate.dtype == a.dtype
     _call("jllm_gemm_heads", a.data_ptr(), _DT[a.dtype], a.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
-          _p(gate), gate.stride(0) if gate is not None else 0, float(alpha), a.shape[0], heads, N, K, _stream())
+          _p(gate), gate.stride(0) if gate is not None else 0, float(alpha), a.shape[0], heads, N, K, int(a_head),
+          int(out_head), _stream())
+
+
+def latent_prepare(src, q_off, q_rank, q_gain, cq, d_off, rank, rope_dim, gain, cos, sin, rotary_dim, positions, slots, cache,
+                   eps, write_latent=True) -> None:
+    """From the float32 rows `src` of a mixer's stacked down projections: cq[r] = rmsnorm(src[r, q_off : q_off + q_rank]) *
+    q_gain (q_rank = 0: no query latent), and, with `write_latent`, the cached row slots[r] = [rmsnorm(src[r, d_off : d_off +
+    rank]) * gain, the rope_dim values behind them with their first rotary_dim values turned in neighbouring pairs by the
+    row's position]. cq and the cache [pages, 1, page_size, rank + rope_dim] have the compute type."""
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and positions.dtype == torch.int32
+    assert cq is None or (cq.is_contiguous() and cq.shape[1] == q_rank)
+    if write_latent:
+        assert cache.is_contiguous() and cache.shape[-1] == rank + rope_dim and slots.dtype == torch.int32
+        assert cq is None or cq.dtype == cache.dtype
+    dtype = cache.dtype if write_latent else cq.dtype
+    _call("jllm_latent_prepare", src.data_ptr(), src.stride(0), int(q_off), int(q_rank), _p(q_gain), _p(cq), int(d_off),
+          int(rank), int(rope_dim), _p(gain), _DT[(gain if gain is not None else q_gain).dtype], _p(cos), _p(sin),
+          int(rotary_dim), positions.data_ptr(), _p(slots) if write_latent else 0, _p(cache) if write_latent else 0, _DT[dtype],
+          cache.numel() // (rank + rope_dim) if write_latent else 0, src.shape[0], float(eps), int(bool(write_latent)), _stream())
+
+
+def rope_heads(q, q_head, q_off, out, out_head, out_off, heads, rope_dim, cos, sin, rotary_dim, positions) -> None:
+    """out[r, h * out_head + out_off + i] = the i-th of head h's rope_dim values q[r, h * q_head + q_off + ...], the first
+    rotary_dim of them turned in neighbouring pairs (2i, 2i + 1) by the row's position."""
+    assert q.dtype == out.dtype and q.stride(1) == 1 and out.stride(1) == 1 and positions.dtype == torch.int32
+    _call("jllm_rope_heads", q.data_ptr(), _DT[q.dtype], q.stride(0), int(q_head), int(q_off), out.data_ptr(), out.stride(0),
+          int(out_head), int(out_off), q.shape[0], int(heads), int(rope_dim), cos.data_ptr(), sin.data_ptr(), int(rotary_dim),
+          positions.data_ptr(), _stream())
+
+
+SWISH_ALPHA = 1.702      # the logistic's slope in the clamped gated unit
+
+
+def glu_clamped(gate_up, weights, out, experts, ff, limit, alpha: float = SWISH_ALPHA) -> None:
+    """out[r, e * ff + j] = g sigmoid(alpha g) (u + 1), g = min(w gate, limit), u = clamp(w up, -limit, limit), w =
+    weights[r, e] (1 without weights); gate_up [rows, 2 x experts x ff]: all gate values, then all up values."""
+    assert gate_up.dtype == out.dtype and gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.shape[1] == 2 * experts * ff and out.shape[1] == experts * ff
+    assert weights is None or (weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape[1] == experts)
+    _call("jllm_glu_clamped", gate_up.data_ptr(), _p(weights), out.data_ptr(), _DT[out.dtype], out.shape[0], int(experts),
+          int(ff), float(limit), float(alpha), _stream())
+
+
+def layernorm(x, gain, eps, out, row_index=None, rows=None, center: bool = True, out_scale: float = 1.0) -> None:
+    """out[r] = (x[s] - mean) / sqrt(variance + eps) * gain * out_scale, s = row_index[r] or r (`center` False: x[s] /
+    sqrt(mean(x^2) + eps)); x float32 [*, dim]; out float32 or bfloat16."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n = (row_index.numel() if row_index is not None else x.shape[0]) if rows is None else rows
+    _call("jllm_layernorm", x.data_ptr(), gain.data_ptr(), _DT[gain.dtype], out.data_ptr(), _DT[out.dtype], _p(row_index), n,
+          x.shape[-1], float(eps), int(bool(center)), float(out_scale), _stream())
+
+
+def norm_add(x, a, gain, eps, next_out=None, center: bool = True) -> None:
+    """x += norm(a) * gain (the layer norm, or with `center` False the RMS norm), and, with `next_out` ([rows, dim], float32
+    or bfloat16), next_out = x in that type. x, a float32 [rows, dim], contiguous."""
+    assert x.dtype == a.dtype == torch.float32 and x.is_contiguous() and a.is_contiguous() and x.shape == a.shape
+    assert next_out is None or (next_out.is_contiguous() and next_out.shape == x.shape)
+    _call("jllm_norm_add", x.data_ptr(), a.data_ptr(), gain.data_ptr(), _DT[gain.dtype], _p(next_out),
+          _DT[next_out.dtype] if next_out is not None else F32, x.shape[0], x.shape[1], float(eps), int(bool(center)), _stream())
+
+
+def token_shift(x, mu, state, batch, out) -> None:
+    """out[r] = x[r] + (p - x[r]) * mu, p the row in front of r in its request: x[r - 1], or for a segment's first row what
+    `state[batch.state_slots[segment]]` holds (the row the step before saved; zeros for a new request). The last row of every
+    segment is saved there for the next step (a second launch unless every segment is one row)."""
+    global launch_count
+    assert x.dtype == state.dtype == torch.float32 and x.is_contiguous() and state.is_contiguous() and out.is_contiguous()
+    assert state.shape[1] == x.shape[1] == out.shape[1]
+    single = batch.decode_only
+    launch_count += 0 if single else 1
+    _call("jllm_token_shift", x.data_ptr(), mu.data_ptr(), _DT[mu.dtype], state.data_ptr(), state.shape[0],
+          batch.row_seg.data_ptr(), batch.seg_start.data_ptr(), batch.seg_len.data_ptr(), batch.state_slots.data_ptr(),
+          out.data_ptr(), _DT[out.dtype], x.shape[0], batch.seg_start.numel(), x.shape[1], int(single), _stream())
+
+
+def depth_mix(stack, weights, n, out) -> None:
+    """out = sum over j < n of weights[j] * stack[j] (ascending j); stack float32 [planes, rows, dim], whose planes may be
+    further apart than out's rows x dim values; out float32, contiguous."""
+    assert stack.dtype == out.dtype == torch.float32 and out.is_contiguous() and weights.numel() >= n and stack.shape[0] >= n
+    assert stack.stride(2) == 1 and stack.stride(1) == stack.shape[2] == out.shape[-1]
+    _call("jllm_depth_mix", stack.data_ptr(), stack.stride(0), weights.data_ptr(), _DT[weights.dtype], int(n), out.data_ptr(),
+          out.numel(), _stream())
+
+
+def scale_values(x, s: float) -> None:
+    """x *= s, float32 and contiguous."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _call("jllm_scale_values", x.data_ptr(), float(s), x.numel(), _stream())
 
 
 def route_experts(h, router, correction, top, scale, normalize, weights) -> None:
@@ -312,6 +412,20 @@ def scale_expert_hidden(hidden, weights, ff) -> None:
 
 
 GLU_KINDS = {"silu": 1, "gelu_tanh": 2}      # the gate's activation as the kernels number it (GLU_* in common.cuh)
+
+
+def glu_descriptor(activation: str, limit: float = 0.0) -> int:
+    """What a product's `swiglu` argument is for a gated feed-forward of this activation: the activation's number, or, for the
+    clamped unit, a word that carries its number (3) in the two lowest bits and the limit's float32 bits above them (the
+    limit's two last mantissa bits are dropped: a change of at most 3 parts in ten million, in an epilogue whose results are
+    rounded to bfloat16)."""
+    if activation != "swish_clamped":
+        return GLU_KINDS[activation]
+    import struct
+    (bits,) = struct.unpack("<i", struct.pack("<f", float(limit)))
+    if not limit > 0:
+        raise KernelError(f"the clamped gated unit needs a positive limit, got {limit}")
+    return (bits & ~3) | 3
 
 
 def glu_kind(activation) -> int:
@@ -638,7 +752,7 @@ def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swigl
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
-                "attention_prefill_pair", "rowwise", "linear_attention", "latent_attention")
+                "attention_prefill_pair", "rowwise", "linear_attention", "latent_attention", "residual_paths")
 BOUNDS_WHAT = {1: "a block-table index", 2: "a page id", 3: "a cache slot", 4: "a token id", 5: "a row"}
 
 

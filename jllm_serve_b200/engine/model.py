@@ -14,7 +14,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..config.specs import Decoder
+from ..cache.manager import needs_of
+from ..config.specs import ConfigError, Decoder
 from ..csrc import ops
 from ..parts import Linear, RunCache, Runtime, part_class
 from ..weights.loader import TensorWant
@@ -49,6 +50,28 @@ class DecoderModel:
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, core.dim, tensors,
                                                                    names.final_norm, runtime)
         self.vocab, self.dim = core.vocab, core.dim
+        self.logit_scale = float(getattr(core, "logit_scale", 1.0))
+        # depth mix: what run i hands on is a weighted sum of the embedded rows and of every run's result so far
+        self.depth_weights = None
+        if getattr(spec, "depth_mix", ""):
+            self.depth_weights = [tensors[name] for name in self._depth_names(spec)]
+            self._one = torch.ones(1, dtype=torch.float32, device=runtime.device)
+        # how many of a run's fixed-size states are its arrangement's own (they follow the mixer's in the run's list)
+        self._block_states = [len(needs_of(self._block_need(spec, spec.layers[run.layer]))) for run in spec.schedule]
+
+    @staticmethod
+    def _block_need(spec: Decoder, layer):
+        need = getattr(part_class("block", layer.arrangement), "cache_need", None)
+        return need(layer, spec.core.dim) if need is not None else None
+
+    @staticmethod
+    def _depth_names(spec: Decoder) -> List[str]:
+        """The tensor of run i's i + 2 depth weights lies under the prefix of the layer that run i runs; a layer that runs
+        twice would need two tensors of one name."""
+        names = [cls_prefix(spec.layers[run.layer], spec.names, run.layer) + spec.depth_mix for run in spec.schedule]
+        if len(set(names)) != len(names):
+            raise ConfigError("a depth mix needs weights per layer run, and a layer that runs twice has one tensor")
+        return names
 
     @classmethod
     def wants(cls, spec: Decoder) -> Dict[str, TensorWant]:
@@ -61,6 +84,9 @@ class DecoderModel:
         for l, layer in enumerate(spec.layers):
             out.update(part_class("block", layer.arrangement).wants(layer, core.dim, cls_prefix(layer, names, l)))
         out.update(part_class("norm", spec.final_norm.kind).wants(spec.final_norm, core.dim, names.final_norm))
+        if getattr(spec, "depth_mix", ""):
+            for i, name in enumerate(cls._depth_names(spec)):
+                out[name] = TensorWant((i + 2,), "vector", init="average")
         return out
 
     @property
@@ -77,8 +103,11 @@ class DecoderModel:
         tuple if the mixer keeps several things, say paged keys and values and a state of fixed size)."""
         needs = []
         for run in self.spec.schedule:
-            mixer = self.spec.layers[run.layer].mixer
-            needs.append(None if run.cache_of is not None else part_class("mixer", mixer.kind).cache_need(mixer))
+            layer = self.spec.layers[run.layer]
+            mixer = layer.mixer
+            need = None if run.cache_of is not None else part_class("mixer", mixer.kind).cache_need(mixer)
+            own = needs_of(self._block_need(self.spec, layer))       # the arrangement's own: kept by every run, borrower or not
+            needs.append(tuple(needs_of(need)) + tuple(own) if own else need)
         return needs
 
     def _run_cache(self, cache, i: int) -> RunCache:
@@ -88,21 +117,38 @@ class DecoderModel:
         if owner in cache.paged_of_run:
             out.group = cache.paged_of_run[owner]
             out.keys, out.values = cache.keys_values(owner)
+        mine, theirs = self._block_states[i], self._block_states[owner]
         states = cache.states(owner)
+        states = states[:len(states) - theirs] if theirs else states
         if states:
             out.states, out.state = tuple(states), states[0]
+        if mine:
+            out.block_states = tuple(cache.states(i)[-mine:])
         return out
 
     def forward(self, batch, cache, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the batch's rows through every scheduled layer; returns float32 logits [wanted rows, vocab]."""
         rows = batch.rows
-        x = self.rt.buffer("residual", self.dim, torch.float32)[:rows]
+        schedule, normed = self.spec.schedule, False
+        stack = None
+        if self.depth_weights is not None:
+            # plane 0: the embedded rows; plane j + 1: run j's result, made in place from the mix that run j was handed
+            # (which the mix kernel wrote there); the last plane: what the last run hands on
+            planes = len(schedule) + 2
+            stack = self.rt.buffer("depth_stack", self.dim, torch.float32, rows=planes * self.rt.max_rows)
+            stack = stack.view(planes, self.rt.max_rows, self.dim)[:, :rows]
+            x = stack[0]
+        else:
+            x = self.rt.buffer("residual", self.dim, torch.float32)[:rows]
         ops.embed_rows(batch.token_ids, self.embedding, x)
         for pe in self.position_encodings:
             pe.on_embedding(x, batch)
-        schedule, normed = self.spec.schedule, False
         for i, run in enumerate(schedule):
             block = self.blocks[run.layer]
+            if stack is not None:
+                if i == 0:
+                    ops.depth_mix(stack, self._one, 1, stack[1])       # the first run reads the embedded rows themselves
+                x = stack[i + 1]
             if getattr(block, "chains_norms", False):
                 # an arrangement whose last launch can also make the next block's normed input is given that block's gain
                 nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
@@ -111,6 +157,9 @@ class DecoderModel:
             else:
                 block.forward(x, batch, self._run_cache(cache, i))
                 normed = False
+            if stack is not None:
+                ops.depth_mix(stack, self.depth_weights[i], i + 2, stack[i + 2])
+                x = stack[i + 2]
         n = batch.num_wanted
         if logits_out is None:
             logits_out = torch.empty((n, self.vocab), dtype=torch.float32, device=self.rt.device)
@@ -119,6 +168,8 @@ class DecoderModel:
         hb = self.rt.buffer("head_in", self.dim)[:n]
         self.final_norm.forward(x, hb, row_index=batch.logit_rows, rows=n)
         self.head.forward(hb, logits_out[:n])
+        if self.logit_scale != 1.0:
+            ops.scale_values(logits_out[:n], self.logit_scale)
         return logits_out[:n]
 
 

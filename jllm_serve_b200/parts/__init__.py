@@ -2,7 +2,7 @@
 from .base import (Block, FeedForward, Mixer, Norm, Part, PositionEncoding, RunCache, Runtime, part_class,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position_encoding)
 from .linear import Linear
-from .norm import DynamicTanh, RmsNorm
+from .norm import DynamicTanh, LayerNorm, RmsNorm
 from .rope import RotaryTable
 from .attention import GqaAttention
 from .mlp import DenseGlu
@@ -10,4 +10,4 @@ from .linear_attention import FixedDecayLinearAttention, GatedLinearAttention
 from .parallel import ParallelMixers
 from .latent_attention import LatentAttention
 from .experts import RoutedExperts
-from .block import PreNormBlock, SandwichNormBlock
+from .block import PostNormBlock, PreNormBlock, SandwichNormBlock

@@ -126,6 +126,8 @@ class RunCache:
     state: Optional[torch.Tensor] = None   # [slots, ...] for a fixed-state mixer (the first of `states`)
     states: tuple = ()                     # every fixed-size state the mixer named, in its order; a mixer may hold
                                            # these beside paged keys and values
+    block_states: tuple = ()               # the states the run's arrangement named for itself (always the run's own, also
+                                           # where the mixer reads another run's cache)
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}

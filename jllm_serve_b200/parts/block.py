@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import torch
 
+from ..cache.manager import FixedState
 from ..csrc import ops
 from ..weights.loader import TensorWant
 from .base import Block, part_class, register_block
@@ -173,3 +174,100 @@ class SandwichNormBlock(PreNormBlock):
 
 
 register_block("sandwich_norm", SandwichNormBlock, replace=True)
+
+
+class PostNormBlock(Block):
+    """The norm sits behind each part, on the part's result, and the parts read the stream itself:
+
+        x += norm(mixer(h));   x += norm'(feed_forward(x)),   h = x, or with a token shift x_t + (x_(t-1) - x_t) * mu
+
+    The norm is the layer's (`layernorm` or `rmsnorm`, gains `names.mixer_norm` and `names.feed_forward_norm`). A part writes
+    its result into a float32 buffer (`overwrite`; one that cannot gets it zeroed) and one kernel norms it, adds it to the
+    stream and, in bfloat16, leaves the stream's new rows in the compute type for the part that follows. With a token shift
+    the block keeps one row of the stream per request between steps (`cache_need`: a state of `dim` float32 values; the
+    cache manager hands a new request a zeroed one), which is what a segment's first row blends with."""
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, position_encodings):
+        names, gain = spec.names, getattr(spec.norm, "gain_name", "weight")
+        if spec.norm.kind not in ("layernorm", "rmsnorm"):
+            raise ValueError(f"the norm behind a part is a layer norm or an RMS norm; the layer's is {spec.norm.kind!r}")
+        if float(getattr(spec, "residual_scale", 1.0)) != 1.0:
+            raise ValueError("a residual scale together with norms behind the parts is not built")
+        self.rt, self.dim, self.eps, self.center = runtime, dim, float(spec.norm.eps), spec.norm.kind == "layernorm"
+        self.mixer_gain = tensors[prefix + names.mixer_norm + gain]
+        mixer_cls = part_class("mixer", spec.mixer.kind)
+        table = getattr(spec.mixer, "rope_table", -1)
+        extra = {"rope": position_encodings[table]} if table is not None and table >= 0 and position_encodings else {}
+        if getattr(mixer_cls, "wants_position_encodings", False):
+            extra = {"position_encodings": position_encodings}
+        self.mixer = mixer_cls(spec.mixer, dim, tensors, prefix + names.mixer, runtime, **extra)
+        self.ffn_gain = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ffn_gain = tensors[prefix + names.feed_forward_norm + gain]
+            self.feed_forward = part_class("feed_forward", spec.feed_forward.kind)(
+                spec.feed_forward, dim, tensors, prefix + names.feed_forward, runtime)
+        self.shift = tensors[prefix + spec.token_shift] if spec.token_shift else None
+        self._zero_first = set()
+        for part in (self.mixer, self.feed_forward):
+            if part is None:
+                continue
+            if getattr(part, "can_overwrite", False):
+                part.overwrite = True
+            else:
+                self._zero_first.add(id(part))
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feed_forward) if p is not None)
+
+    def decode_bucket_cap(self, rows: int) -> int:
+        return getattr(self.mixer, "decode_bucket_cap", lambda _: 32)(rows)
+
+    @classmethod
+    def cache_need(cls, spec, dim: int):
+        """What the arrangement itself keeps between steps, beside its mixer's need."""
+        return FixedState((dim,), "float32") if spec.token_shift else None
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        names, gain = spec.names, getattr(spec.norm, "gain_name", "weight")
+        out = {prefix + names.mixer_norm + gain: TensorWant((dim,), "vector", init="gain")}
+        out.update(part_class("mixer", spec.mixer.kind).wants(spec.mixer, dim, prefix + names.mixer))
+        if spec.feed_forward is not None:
+            out[prefix + names.feed_forward_norm + gain] = TensorWant((dim,), "vector", init="gain")
+            out.update(part_class("feed_forward", spec.feed_forward.kind).wants(spec.feed_forward, dim,
+                                                                                prefix + names.feed_forward))
+        if spec.token_shift:
+            out[prefix + spec.token_shift] = TensorWant((dim,), "vector")
+        return out
+
+    def _result(self, part, rows):
+        y = self.rt.buffer("part_result", self.dim, torch.float32)[:rows]
+        if id(part) in self._zero_first:
+            y.zero_()
+        return y
+
+    def forward(self, x, batch, cache) -> None:
+        rows = x.shape[0]
+        low = self.rt.dtype != torch.float32            # the parts read a copy of the stream in the compute type
+        xb = self.rt.buffer("normed", self.dim)[:rows]
+        if self.shift is not None:
+            ops.token_shift(x, self.shift, cache.block_states[0], batch, xb)
+            h = xb
+        elif low:
+            xb.copy_(x)
+            h = xb
+        else:
+            h = x
+        a = self._result(self.mixer, rows)
+        self.mixer.forward(h, a, batch, cache)
+        if self.feed_forward is None:
+            ops.norm_add(x, a, self.mixer_gain, self.eps, center=self.center)
+            return
+        ops.norm_add(x, a, self.mixer_gain, self.eps, next_out=xb if low else None, center=self.center)
+        y = self._result(self.feed_forward, rows)
+        self.feed_forward.forward(xb if low else x, y, batch)
+        ops.norm_add(x, y, self.ffn_gain, self.eps, center=self.center)
+
+
+register_block("post_norm", PostNormBlock, replace=True)

@@ -8,6 +8,12 @@ two, a row's hidden values of expert e are multiplied by its weight (and by the 
 does not use contributes exact zeros, and the sum over experts is the product's own float32 accumulation. Every weight
 streams once per step however the rows choose; what this costs against running only the chosen experts is experts / top
 times the multiply-adds.
+
+`weight_on` "input" (with the clamped gated unit): a row's weight multiplies what the expert READS, y = sum_e expert_e(w_e h).
+Both of an expert's first products are linear, so w_e (Wgate_e h) and w_e (Wup_e h) are what it would have computed: the
+stacked product runs once on h itself, and one kernel (`ops.glu_clamped`) multiplies, cuts off and gates. An expert that a
+row does not use has weight 0 and adds exact zeros, as above. `shared`: a dense gated feed-forward of its own sizes that
+every row runs, added to the same result.
 """
 from __future__ import annotations
 
@@ -15,21 +21,28 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import TensorWant
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, part_class, register_feed_forward
 from .linear import Linear
 
 
 class RoutedExperts(FeedForward):
     takes_residual_scale = True
+    can_overwrite = True           # a block that norms the result before adding it asks for x = ... instead of x += ...
 
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
         self.spec, self.dim, self.rt = spec, dim, runtime
         self.residual_scale = 1.0
+        self.overwrite = False
         E, ff = spec.experts, spec.hidden
         self.hidden = E * ff
+        self.on_input = getattr(spec, "weight_on", "output") == "input"
+        self.shared = None
+        if getattr(spec, "shared", None) is not None:
+            self.shared = part_class("feed_forward", spec.shared.kind)(spec.shared, dim, tensors, prefix + "shared.", runtime)
         gate = torch.cat([tensors.pop(f"{prefix}e{e}.gate") for e in range(E)], dim=0)
         up = torch.cat([tensors.pop(f"{prefix}e{e}.up") for e in range(E)], dim=0)
-        self.fused = gate.dtype == torch.bfloat16 and dim % 8 == 0 and self.hidden % 8 == 0
+        # (a weight in front of the gated unit rules out the product's own epilogue, which gates what it has summed)
+        self.fused = gate.dtype == torch.bfloat16 and dim % 8 == 0 and self.hidden % 8 == 0 and not self.on_input
         if self.fused:      # blocks of 8 gate rows followed by their 8 up rows: the product's epilogue applies SwiGLU
             stacked = torch.stack([gate.view(self.hidden // 8, 8, dim), up.view(self.hidden // 8, 8, dim)], dim=1)
             self.gate_up = Linear(stacked.reshape(2 * self.hidden, dim).contiguous())
@@ -50,6 +63,8 @@ class RoutedExperts(FeedForward):
             out[f"{prefix}e{e}.gate"] = TensorWant((spec.hidden, dim))
             out[f"{prefix}e{e}.up"] = TensorWant((spec.hidden, dim))
             out[f"{prefix}e{e}.down"] = TensorWant((dim, spec.hidden))
+        if getattr(spec, "shared", None) is not None:
+            out.update(part_class("feed_forward", spec.shared.kind).wants(spec.shared, dim, prefix + "shared."))
         return out
 
     def forward(self, xb, x, batch) -> None:
@@ -57,14 +72,21 @@ class RoutedExperts(FeedForward):
         weights = self.rt.buffer("expert_weights", s.experts, torch.float32)[:rows]
         ops.route_experts(xb, self.router, self.correction, s.top, s.scale * self.residual_scale, s.normalize, weights)
         h = self.rt.buffer("experts_hidden", self.hidden)[:rows]
-        if self.fused:
-            self.gate_up.forward(xb, h, swiglu=True)
-        else:
+        if self.on_input:
             gate_up = self.rt.buffer("experts_gate_up", 2 * self.hidden)[:rows]
             self.gate_up.forward(xb, gate_up)
-            ops.swiglu(gate_up, h)
-        ops.scale_expert_hidden(h, weights, s.hidden)
-        self.down.forward(h, x, accumulate=True)
+            ops.glu_clamped(gate_up, weights, h, s.experts, s.hidden, s.limit)
+        else:
+            if self.fused:
+                self.gate_up.forward(xb, h, swiglu=True)
+            else:
+                gate_up = self.rt.buffer("experts_gate_up", 2 * self.hidden)[:rows]
+                self.gate_up.forward(xb, gate_up)
+                ops.swiglu(gate_up, h)
+            ops.scale_expert_hidden(h, weights, s.hidden)
+        self.down.forward(h, x, accumulate=not self.overwrite)
+        if self.shared is not None:
+            self.shared.forward(xb, x, batch)          # (adds: its `overwrite` stays off)
 
 
 register_feed_forward("routed_experts", RoutedExperts, replace=True)

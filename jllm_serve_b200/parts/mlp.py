@@ -1,4 +1,5 @@
-"""The dense gated feed-forward: x += Wdown (act(Wgate xb) * (Wup xb)), act = silu or the tanh form of GELU.
+"""The dense gated feed-forward: x += Wdown (act(Wgate xb) * (Wup xb)), act = silu or the tanh form of GELU; or, as
+`swish_clamped`, x += Wdown (g sigmoid(1.702 g) (u + 1)) with g = min(Wgate xb, limit) and u = clamp(Wup xb, -limit, limit).
 
 Formula from the reference (src/main/java/org/robomiri/jllm/cpu/CpuBackend.java:661-669,
 silu at cpu/VectorKernels.java:637-639). As the reference's converter does
@@ -21,7 +22,10 @@ class DenseGlu(FeedForward):
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
         self.hidden, self.dim, self.rt = spec.hidden, dim, runtime
         names = getattr(spec, "names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
-        self.activation = getattr(spec, "activation", "silu")      # silu | gelu_tanh: the kernels' epilogues take either
+        self.activation = getattr(spec, "activation", "silu")      # silu | gelu_tanh | swish_clamped: the kernels' epilogues take any
+        self.limit = float(getattr(spec, "limit", 0.0))
+        # what the products' epilogues are told: the activation's number, or for the clamped unit its number and limit
+        self.glu = ops.glu_descriptor(self.activation, self.limit)
         self.overwrite = False                                      # True: the result replaces x instead of being added to it
         gate, up = tensors.pop(prefix + names[0]), tensors.pop(prefix + names[1])
         # bfloat16: blocks of 8 gate rows followed by their 8 up rows, so that the product's epilogue holds a
@@ -47,11 +51,14 @@ class DenseGlu(FeedForward):
         rows = xb.shape[0]
         h = self.rt.buffer("ffn_hidden", self.hidden)[:rows]
         if self.fused:
-            self.gate_up.forward(xb, h, swiglu=self.activation)
+            self.gate_up.forward(xb, h, swiglu=self.glu)
         else:
             gate_up = self.rt.buffer("gate_up", 2 * self.hidden)[:rows]
             self.gate_up.forward(xb, gate_up)
-            ops.swiglu(gate_up, h, self.activation)
+            if self.activation == "swish_clamped":
+                ops.glu_clamped(gate_up, None, h, 1, self.hidden, self.limit)
+            else:
+                ops.swiglu(gate_up, h, self.activation)
         self.down.forward(h, x, accumulate=not self.overwrite)
 
 

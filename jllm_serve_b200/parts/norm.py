@@ -50,3 +50,23 @@ class DynamicTanh(Norm):
 
 
 register_norm("dynamic_tanh", DynamicTanh, replace=True)
+
+
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(variance + eps) * w, the variance being the mean of the squared deviations; a weight and no
+    bias. Float32 arithmetic; the output has the compute dtype. `out_scale` multiplies the result (1 unless a model sets it)."""
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
+        self.eps = float(spec.eps)
+        self.dim = dim
+        self.gain = tensors[prefix + getattr(spec, "gain_name", "weight")]
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        return {prefix + getattr(spec, "gain_name", "weight"): TensorWant((dim,), "vector", init="gain")}
+
+    def forward(self, x, out, row_index=None, rows=None):
+        ops.layernorm(x, self.gain, self.eps, out, row_index, rows, center=True)
+
+
+register_norm("layernorm", LayerNorm, replace=True)

@@ -44,7 +44,8 @@ class TensorWant:
     shape: Tuple[int, ...]                 # a size of -1: the checkpoint's own (the part reads it from the tensor)
     role: str = "matrix"                   # matrix | matrix_fp32 | vector | int_table
     optional: bool = False
-    init: str = "normal"                   # random-weights mode: normal = N(0, 0.02), gain = 1 + N(0, 0.1)
+    init: str = "normal"                   # random-weights mode: normal = N(0, 0.02), gain = 1 + N(0, 0.1),
+                                           # average = (1 + N(0, 0.1)) / the tensor's size
 
 
 def target_dtype(stored: torch.dtype, role: str, compute: torch.dtype) -> torch.dtype:

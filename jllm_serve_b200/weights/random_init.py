@@ -40,7 +40,10 @@ def random_tensors(wants: Dict[str, TensorWant], seed: int, device="cpu", dtype:
                              f"({list(want.shape)}); random weights need it named")
         gen.manual_seed(_seed_for(seed, name))
         t = torch.randn(want.shape, generator=gen, device=device, dtype=torch.float32)
-        t = t * GAIN_STD + 1.0 if want.init == "gain" else t * MATRIX_STD
+        if want.init == "average":          # weights of a weighted mean: about 1 / n each
+            t = (t * GAIN_STD + 1.0) / max(1, t.numel())
+        else:
+            t = t * GAIN_STD + 1.0 if want.init == "gain" else t * MATRIX_STD
         to = (vector_dtype or dtype) if want.role == "vector" else dtype
         out[name] = t.to(torch.int32) if want.role == "int_table" else t.to(to)
     return out
