@@ -13,10 +13,11 @@ read (every weight once plus the cache of the live requests) with the measured c
 `points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
 layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
 
-`--design madevik` and `--design movivik` are another program under the same roof and leave the default workload alone:
-prefill and decode of the Madevik design (gated linear attention, attention over a cached latent, routed experts) or of
-the Movivik design (chunked and parallel attention layers, linear attention with fixed decays, norms in front of and behind
-every part) at layer sizes that resemble a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
+`--design madevik`, `--design movivik` and `--design bozevik` are another program under the same roof and leave the default
+workload alone: prefill and decode of the Madevik design (gated linear attention, attention over a cached latent, routed
+experts), of the Movivik design (chunked and parallel attention layers, linear attention with fixed decays, norms in front of
+and behind every part) or of the Bozevik design (attention over a cached latent with a query latent and a shared rotated key
+part, layer norms behind the parts, token shift, depth mix, clamped gated units) at layer sizes that resemble a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
 picks among them); one JSON line with both models' figures per size.
 
 The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
@@ -142,17 +143,47 @@ def movivik_shape(width, heads, kv_heads, ff, runs, chunk=1024, vocab=32768):
             "layers": [att if i % 4 < 2 else par for i in range(runs)]}
 
 
+def bozevik_shape(width, heads, rank, rot, q_rank, experts, top, ff, dense_ff, runs, vocab=32768):
+    """Attention over a cached latent in every layer (queries through a latent of `q_rank` values, a rotated key part of `rot`
+    values beside a latent of `rank`; every second layer reads the rows the layer in front of it cached), head size 128; dense
+    and routed feed-forwards (with a shared expert) take turns."""
+    def mixer(i):
+        m = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": rank, "q_rank": q_rank, "rot_dim": rot,
+             "rot": {"base": 10000.0, "dims": rot}, "scale": (128 + rot) ** -0.5}
+        return dict(m, kv_from=i - 1) if i % 2 else m
+    dense = {"kind": "dense", "ff": dense_ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": ff, "limit": 7.0}}
+    return {"architecture": "Bozevik", "width": width, "vocab": vocab, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": mixer(i), "mlp": moe if i % 2 else dense} for i in range(runs)]}
+
+
+def madevik_latent_shape(width, heads, rank, experts, top, ff, runs, vocab=32768):
+    """A Madevik model of latent-attention layers only (the closest kin of the Bozevik shape): cached rows of `rank` values."""
+    latent = {"type": "latent_attention", "mlp": _moe(experts, top, ff),
+              "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": rank, "scale": 128 ** -0.5}}
+    return {"architecture": "Madevik", "width": width, "vocab": vocab, "residual_mult": 0.7, "norm": {"eps": 1e-6},
+            "layers": [latent for _ in range(runs)]}
+
+
 def _qwen3_shape(width, layers, heads, kv_heads, ffn):
     return dict(QWEN3_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
                 intermediate_size=ffn, vocab_size=32768)
 
 
-# design -> name -> (the design's configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward weights)
+# design -> name -> (the design's configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward
+# weights[, a third configuration and its label: the design's closest kin among the other designs])
 DESIGN_SIZES = {
     "madevik": {"w2048": (madevik_shape(2048, 16, 128, 8, 2, 1024, 8), _qwen3_shape(2048, 8, 16, 8, 8192)),
                 "w4096": (madevik_shape(4096, 32, 256, 16, 4, 768, 4), _qwen3_shape(4096, 4, 32, 8, 12288))},
     "movivik": {"w2048": (movivik_shape(2048, 16, 8, 8192, 8), _qwen3_shape(2048, 8, 16, 8, 8192)),
                 "w4096": (movivik_shape(4096, 32, 8, 12288, 4), _qwen3_shape(4096, 4, 32, 8, 12288))},
+    # cached rows of 192 + 64 and of 96 + 32 values; beside each the Qwen3 shape and a Madevik model of latent-attention
+    # layers with cached rows of the same width and the same experts
+    "bozevik": {"w2048": (bozevik_shape(2048, 16, 192, 64, 768, 8, 2, 1024, 8192, 8), _qwen3_shape(2048, 8, 16, 8, 8192),
+                          madevik_latent_shape(2048, 16, 256, 8, 2, 1024, 8), "madevik_latent"),
+                "w4096": (bozevik_shape(4096, 32, 96, 32, 1536, 16, 4, 768, 12288, 4), _qwen3_shape(4096, 4, 32, 8, 12288),
+                          madevik_latent_shape(4096, 32, 128, 16, 4, 768, 4), "madevik_latent")},
 }
 
 
@@ -175,7 +206,8 @@ def design_bench(args) -> int:
             print(f"bench.py: unknown size {name!r} (known: {', '.join(sorted(sizes))})")
             return 2
         record = {}
-        for model, cfg in zip((args.design, "qwen3"), sizes[name]):
+        entry = sizes[name]
+        for model, cfg in zip((args.design, "qwen3") + tuple(entry[3:4]), entry[:3]):
             engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx + 64, page_size=PAGE,
                             num_pages=((batch + 1) * (ctx + 64) + 2 * tokens) // PAGE, max_batch_tokens=tokens + 64,
                             chunk=tokens, max_running=batch + 2)
@@ -257,8 +289,9 @@ def _tensors_of(obj, seen=None):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("--design", default="", choices=["", "madevik", "movivik"],
-                    help="madevik, movivik: time that design beside the Qwen3 dense shape of equal size instead of the default workload")
+    ap.add_argument("--design", default="", choices=["", "madevik", "movivik", "bozevik"],
+                    help="madevik, movivik, bozevik: time that design beside the Qwen3 dense shape of equal size (bozevik: also "
+                         "beside a Madevik model of latent-attention layers) instead of the default workload")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of the sizes of --design, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -112,40 +112,97 @@ __global__ void scale_expert_hidden_vec_kernel(T* __restrict__ hidden, const flo
 // The gated unit whose two inputs are cut off: g = min(w gate, limit), u = clamp(w up, -limit, limit), y = g sigmoid(alpha g)
 // (u + 1); w the row's weight for the expert the unit belongs to (the weight multiplies the expert's INPUT, which by
 // linearity of the two products is the same as multiplying their results), 1 without a weight table. gate_up [rows,
-// 2 * experts * ff]: all gate values, then all up values. An expert the row does not use (w = 0) gives exact zeros.
+// 2 * width]: all gate values, then all up values; width = experts * ff + shared_ff: behind the experts' units may lie
+// those of a shared expert that every row uses with weight 1 and a limit of its own. An expert the row does not use
+// (w = 0) gives exact zeros.
+__device__ __forceinline__ float clamped_unit(float gate, float up, float w, float limit, float alpha) {
+    const float g = fminf(__fmul_rn(w, gate), limit);
+    const float u = fminf(fmaxf(__fmul_rn(w, up), -limit), limit);
+    return __fmul_rn(g / (1.f + expf(-__fmul_rn(alpha, g))), u + 1.f);
+}
+
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights, T* __restrict__ out,
-                                   int experts, int ff, float limit, float alpha, size_t total) {
+                                   int experts, int ff, float limit, int shared_ff, float shared_limit, float alpha,
+                                   size_t total) {
     pdl_wait();
     pdl_trigger();
-    const size_t width = (size_t)experts * ff;
+    const size_t routed = (size_t)experts * ff, width = routed + shared_ff;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / width, col = i - r * width;
-        const float w = weights ? weights[r * experts + col / ff] : 1.f;
+        const bool own = col < routed;
+        const float w = own && weights ? weights[r * experts + col / ff] : 1.f;
         const T* row = gate_up + r * 2 * width;
-        const float g = fminf(__fmul_rn(w, to_float(row[col])), limit);
-        const float u = fminf(fmaxf(__fmul_rn(w, to_float(row[width + col])), -limit), limit);
-        out[i] = from_float<T>(__fmul_rn(g / (1.f + expf(-__fmul_rn(alpha, g))), u + 1.f));
+        out[i] = from_float<T>(clamped_unit(to_float(row[col]), to_float(row[width + col]), w, own ? limit : shared_limit, alpha));
+    }
+}
+
+// The same, 16 bytes a thread (ff and shared_ff multiples of the 16-byte group: a group lies inside one expert).
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_vec_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights, T* __restrict__ out, int experts, int ff,
+                       float limit, int shared_ff, float shared_limit, float alpha, int rows) {
+    constexpr int N = 16 / sizeof(T);
+    pdl_wait();
+    pdl_trigger();
+    const int routed = experts * ff, width = routed + shared_ff, groups = width / N;
+    const int r = blockIdx.y;
+    if (r >= rows) return;
+    const T* row = gate_up + (size_t)r * 2 * width;
+    T* dst = out + (size_t)r * width;
+    for (int gi = blockIdx.x * blockDim.x + threadIdx.x; gi < groups; gi += gridDim.x * blockDim.x) {
+        const int col = gi * N;
+        const bool own = col < routed;
+        const float w = own && weights ? weights[(size_t)r * experts + col / ff] : 1.f;
+        uint4 res;
+        T* y = reinterpret_cast<T*>(&res);
+        if (w == 0.f) {         // the row does not use this expert: its units are not read
+#pragma unroll
+            for (int k = 0; k < N; ++k) y[k] = from_float<T>(0.f);
+        } else {
+            const uint4 graw = *reinterpret_cast<const uint4*>(row + col), uraw = *reinterpret_cast<const uint4*>(row + width + col);
+            const T* g = reinterpret_cast<const T*>(&graw);
+            const T* u = reinterpret_cast<const T*>(&uraw);
+            const float lim = own ? limit : shared_limit;
+#pragma unroll
+            for (int k = 0; k < N; ++k) y[k] = from_float<T>(clamped_unit(to_float(g[k]), to_float(u[k]), w, lim, alpha));
+        }
+        *reinterpret_cast<uint4*>(dst + col) = res;
     }
 }
 
 }  // namespace
 
-// gate_up [rows, 2 * experts * ff], out [rows, experts * ff], both contiguous and of type `dtype`; weights [rows, experts]
-// float32 or null.
+// gate_up [rows, 2 * (experts * ff + shared_ff)], out [rows, experts * ff + shared_ff], both contiguous and of type
+// `dtype`; weights [rows, experts] float32 or null.
 JLLM_EXPORT int jllm_glu_clamped(const void* gate_up, const float* weights, void* out, int dtype, int rows, int experts, int ff,
-                                 float limit, float alpha, cudaStream_t stream) {
-    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0 && limit > 0.f, "glu_clamped: rows=%d experts=%d ff=%d limit=%g", rows,
-                 experts, ff, (double)limit);
+                                 float limit, int shared_ff, float shared_limit, float alpha, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0 && limit > 0.f && shared_ff >= 0 && (shared_ff == 0 || shared_limit > 0.f),
+                 "glu_clamped: rows=%d experts=%d ff=%d limit=%g shared_ff=%d shared_limit=%g", rows, experts, ff, (double)limit,
+                 shared_ff, (double)shared_limit);
     if (rows == 0) return JLLM_OK;
-    const size_t total = (size_t)rows * experts * ff;
+    const int width = experts * ff + shared_ff;
+    const int per = dtype == JLLM_F32 ? 4 : 8;
+    if (ff % per == 0 && shared_ff % per == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0 && rows <= 65535) {
+        const dim3 grid(max(1, min(64, (width / per + 255) / 256)), rows);
+        if (dtype == JLLM_F32)
+            jllm_launch(glu_clamped_vec_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)gate_up, weights,
+                        (float*)out, experts, ff, limit, shared_ff, shared_limit, alpha, rows);
+        else
+            jllm_launch(glu_clamped_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                        (const __nv_bfloat16*)gate_up, weights, (__nv_bfloat16*)out, experts, ff, limit, shared_ff, shared_limit,
+                        alpha, rows);
+        return jllm_check_launch("glu_clamped");
+    }
+    const size_t total = (size_t)rows * width;
     const int blocks = (int)min((size_t)65535, (total + 255) / 256);
     if (dtype == JLLM_F32)
         jllm_launch(glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)gate_up, weights,
-                    (float*)out, experts, ff, limit, alpha, total);
+                    (float*)out, experts, ff, limit, shared_ff, shared_limit, alpha, total);
     else
         jllm_launch(glu_clamped_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
-                    (const __nv_bfloat16*)gate_up, weights, (__nv_bfloat16*)out, experts, ff, limit, alpha, total);
+                    (const __nv_bfloat16*)gate_up, weights, (__nv_bfloat16*)out, experts, ff, limit, shared_ff, shared_limit, alpha,
+                    total);
     return jllm_check_launch("glu_clamped");
 }
 

@@ -123,16 +123,51 @@ rope_heads_kernel(const T* __restrict__ q, int ldq, int q_head, int q_off, T* __
     }
 }
 
+// What `gemm_heads` is asked to do beside its product (rope_dim > 0): the rope_dim values that follow a head's K inputs are
+// turned by the row's position and placed behind the head's N outputs. One more block per (row tile, head) does it.
+struct HeadRope {
+    int rope_dim, rotary_dim;
+    const float* cos_t;
+    const float* sin_t;
+    const int* positions;
+};
+
+template <typename T>
+__device__ __forceinline__ void rope_tile(const T* __restrict__ ah, int lda, T* __restrict__ oh, int ldo, int m0, int M, int K, int N,
+                                          const HeadRope& rp) {
+    const int half = rp.rotary_dim / 2, pairs = rp.rope_dim / 2;
+    for (int e = threadIdx.x; e < 64 * pairs; e += blockDim.x) {
+        const int m = m0 + e / pairs, i = e % pairs;
+        if (m >= M) break;
+        const T* src = ah + (size_t)m * lda + K + 2 * i;
+        T* dst = oh + (size_t)m * ldo + N + 2 * i;
+        float a = to_float(src[0]), b = to_float(src[1]);
+        if (i < half) {
+            const size_t at = (size_t)rp.positions[m] * half + i;
+            turn_pair(a, b, rp.cos_t[at], rp.sin_t[at], a, b);
+        }
+        dst[0] = from_float<T>(a);
+        dst[1] = from_float<T>(b);
+    }
+    if (rp.rope_dim & 1)
+        for (int e = threadIdx.x; e < 64 && m0 + e < M; e += blockDim.x)
+            oh[(size_t)(m0 + e) * ldo + N + rp.rope_dim - 1] = ah[(size_t)(m0 + e) * lda + K + rp.rope_dim - 1];
+}
+
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_heads_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, T* __restrict__ out, int ldo,
-                  const T* __restrict__ gate, int ld_gate, float alpha, int M, int N, int K, int a_head, int o_head) {
+                  const T* __restrict__ gate, int ld_gate, float alpha, int M, int N, int K, int a_head, int o_head, HeadRope rp) {
     __shared__ float as[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     pdl_wait();
     pdl_trigger();
+    if (rp.rope_dim > 0 && blockIdx.x == gridDim.x - 1) {
+        rope_tile(a + (size_t)blockIdx.z * a_head, lda, out + (size_t)blockIdx.z * o_head, ldo, blockIdx.y * BM, M, K, N, rp);
+        return;
+    }
     const int tid = threadIdx.x, h = blockIdx.z;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;
@@ -196,11 +231,15 @@ template <bool VEC>
 __global__ void __launch_bounds__(128)
 gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
                       __nv_bfloat16* __restrict__ out, int ldo, const __nv_bfloat16* __restrict__ gate, int ld_gate,
-                      float alpha, int M, int N, int K, int a_head, int o_head) {
+                      float alpha, int M, int N, int K, int a_head, int o_head, HeadRope rp) {
     __shared__ __align__(16) __nv_bfloat16 as[64][HPAD];
     __shared__ __align__(16) __nv_bfloat16 ws[64][HPAD];
     pdl_wait();
     pdl_trigger();
+    if (rp.rope_dim > 0 && blockIdx.x == gridDim.x - 1) {
+        rope_tile(a + (size_t)blockIdx.z * a_head, lda, out + (size_t)blockIdx.z * o_head, ldo, blockIdx.y * 64, M, K, N, rp);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, h = blockIdx.z;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     const __nv_bfloat16* ah = a + (size_t)h * a_head;
@@ -288,29 +327,34 @@ JLLM_EXPORT int jllm_latent_norm_store(const void* src, int dtype, int ld, const
 // a [M, lda] with head h's K values at column h * a_head (0: h * K); w [heads, N, K]; out [M, ldo] with head h's N values at
 // h * o_head (0: h * N); gate (or null) [M, ld_gate] with head h's gate at column h.
 JLLM_EXPORT int jllm_gemm_heads(const void* a, int dtype, int lda, const void* w, void* out, int ldo, const void* gate,
-                                int ld_gate, float alpha, int M, int heads, int N, int K, int a_head, int o_head,
+                                int ld_gate, float alpha, int M, int heads, int N, int K, int a_head, int o_head, int rope_dim,
+                                const float* cos_t, const float* sin_t, int rotary_dim, const int* positions,
                                 cudaStream_t stream) {
     JLLM_REQUIRE(M >= 0 && heads > 0 && N > 0 && K > 0, "gemm_heads: M=%d heads=%d N=%d K=%d", M, heads, N, K);
     if (a_head == 0) a_head = K;
     if (o_head == 0) o_head = N;
+    JLLM_REQUIRE(rope_dim >= 0 && rotary_dim >= 0 && rotary_dim <= rope_dim && rotary_dim % 2 == 0 && a_head >= K + rope_dim &&
+                     o_head >= N + rope_dim && (rope_dim == 0 || positions != nullptr),
+                 "gemm_heads: rope_dim=%d rotary_dim=%d with heads every %d / %d values", rope_dim, rotary_dim, a_head, o_head);
+    const HeadRope rp{rope_dim, rotary_dim, cos_t, sin_t, positions};
     JLLM_REQUIRE(a_head >= K && o_head >= N && lda >= (heads - 1) * a_head + K && ldo >= (heads - 1) * o_head + N &&
                      heads <= 65535 && (M + BM - 1) / BM <= 65535,
                  "gemm_heads: lda=%d ldo=%d for %d heads of K=%d (every %d), N=%d (every %d)", lda, ldo, heads, K, a_head, N, o_head);
     if (M == 0) return JLLM_OK;
-    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
+    const dim3 grid((N + BN - 1) / BN + (rope_dim > 0 ? 1 : 0), (M + BM - 1) / BM, heads);
     static_assert(BM == 64 && BN == 64, "both kernels take 64 x 64 tiles");
     if (dtype == JLLM_F32) {
         jllm_launch(gemm_heads_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)a, lda,
-                    (const float*)w, (float*)out, ldo, (const float*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
+                    (const float*)w, (float*)out, ldo, (const float*)gate, ld_gate, alpha, M, N, K, a_head, o_head, rp);
         return jllm_check_launch("gemm_heads");
     }
     const bool vec = K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
     if (vec)
         jllm_launch(gemm_heads_mma_kernel<true>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head, rp);
     else
         jllm_launch(gemm_heads_mma_kernel<false>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head);
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K, a_head, o_head, rp);
     return jllm_check_launch("gemm_heads");
 }
 

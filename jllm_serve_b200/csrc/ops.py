@@ -165,16 +165,17 @@ class _Signatures:
     jllm_norm_sum = [P, P, P, P, P, I, I, I, F, F, I, P]
     jllm_norm_chain = [P, P, P, P, P, F, P, P, P, I, I, I, I, F, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
-    jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, I, I, P]
+    jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, I, I, I, P, P, I, P, P]
     jllm_latent_prepare = [P, I, I, I, P, P, I, I, I, P, I, P, P, I, P, P, P, I, ctypes.c_longlong, I, F, I, P]
     jllm_rope_heads = [P, I, I, I, I, P, I, I, I, I, I, I, P, P, I, P, P]
-    jllm_glu_clamped = [P, P, P, I, I, I, I, F, F, P]
+    jllm_glu_clamped = [P, P, P, I, I, I, I, F, I, F, F, P]
     jllm_bounds_error_residual_paths = [P]
     jllm_layernorm = [P, P, I, P, I, P, I, I, F, I, F, P]
     jllm_norm_add = [P, P, P, I, P, I, I, I, F, I, P]
     jllm_token_shift = [P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, P]
     jllm_depth_mix = [P, ctypes.c_longlong, P, I, I, P, ctypes.c_longlong, P]
     jllm_scale_values = [P, F, ctypes.c_longlong, P]
+    jllm_norm_add_mix = [P, P, P, I, I, I, F, I, P, ctypes.c_longlong, P, I, I, P, P, I, P, I, P, P, P, I, P]
     jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
     jllm_scale_expert_hidden = [P, I, P, I, I, I, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
@@ -293,18 +294,21 @@ def latent_norm_store(src, gain, eps, slots, cache) -> None:
           slots.data_ptr(), cache.data_ptr(), cache.numel() // rank, src.shape[0], rank, float(eps), _stream())
 
 
-def gemm_heads(a, w, out, gate=None, alpha: float = 1.0, a_head: int = 0, out_head: int = 0) -> None:
+def gemm_heads(a, w, out, gate=None, alpha: float = 1.0, a_head: int = 0, out_head: int = 0, rope=None) -> None:
     """out[r, h, :] = f * w[h] @ a[r, h, :] for all heads at once; a [rows, heads x K] (any row stride), w [heads, N, K]
     contiguous, out [rows, heads x N]; f = alpha, or alpha * sigmoid(gate[r, h]) with gate a view [rows, heads]. `a_head` /
     `out_head`: the distance between the heads of a row where it is more than K / N (a head's values are then the first K of
-    every a_head values of a, and go to the first N of every out_head values of out)."""
+    every a_head values of a, and go to the first N of every out_head values of out). `rope` = (rope_dim, cos, sin, rotary_dim,
+    positions): the rope_dim values behind a head's K inputs go behind its N outputs, their first rotary_dim values turned in
+    neighbouring pairs by the row's position (what `rope_heads` does in a launch of its own)."""
     heads, N, K = w.shape
+    rope_dim, cos, sin, rotary_dim, positions = rope if rope is not None else (0, None, None, 0, None)
     assert a.dtype == w.dtype == out.dtype and w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
     assert a.shape[1] >= (heads - 1) * (a_head or K) + K and out.shape[1] >= (heads - 1) * (out_head or N) + N
     assert gate is None or gate.dtype == a.dtype
     _call("jllm_gemm_heads", a.data_ptr(), _DT[a.dtype], a.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
           _p(gate), gate.stride(0) if gate is not None else 0, float(alpha), a.shape[0], heads, N, K, int(a_head),
-          int(out_head), _stream())
+          int(out_head), int(rope_dim), _p(cos), _p(sin), int(rotary_dim), _p(positions), _stream())
 
 
 def latent_prepare(src, q_off, q_rank, q_gain, cq, d_off, rank, rope_dim, gain, cos, sin, rotary_dim, positions, slots, cache,
@@ -337,14 +341,17 @@ def rope_heads(q, q_head, q_off, out, out_head, out_off, heads, rope_dim, cos, s
 SWISH_ALPHA = 1.702      # the logistic's slope in the clamped gated unit
 
 
-def glu_clamped(gate_up, weights, out, experts, ff, limit, alpha: float = SWISH_ALPHA) -> None:
+def glu_clamped(gate_up, weights, out, experts, ff, limit, shared_ff: int = 0, shared_limit: float = 0.0,
+                alpha: float = SWISH_ALPHA) -> None:
     """out[r, e * ff + j] = g sigmoid(alpha g) (u + 1), g = min(w gate, limit), u = clamp(w up, -limit, limit), w =
-    weights[r, e] (1 without weights); gate_up [rows, 2 x experts x ff]: all gate values, then all up values."""
+    weights[r, e] (1 without weights); gate_up [rows, 2 x width]: all gate values, then all up values; width = experts x ff +
+    shared_ff, the last shared_ff units being a shared expert's, which every row uses with weight 1 and `shared_limit`."""
+    width = experts * ff + shared_ff
     assert gate_up.dtype == out.dtype and gate_up.is_contiguous() and out.is_contiguous()
-    assert gate_up.shape[1] == 2 * experts * ff and out.shape[1] == experts * ff
+    assert gate_up.shape[1] == 2 * width and out.shape[1] == width
     assert weights is None or (weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape[1] == experts)
     _call("jllm_glu_clamped", gate_up.data_ptr(), _p(weights), out.data_ptr(), _DT[out.dtype], out.shape[0], int(experts),
-          int(ff), float(limit), float(alpha), _stream())
+          int(ff), float(limit), int(shared_ff), float(shared_limit), float(alpha), _stream())
 
 
 def layernorm(x, gain, eps, out, row_index=None, rows=None, center: bool = True, out_scale: float = 1.0) -> None:
@@ -386,6 +393,24 @@ def depth_mix(stack, weights, n, out) -> None:
     assert stack.stride(2) == 1 and stack.stride(1) == stack.shape[2] == out.shape[-1]
     _call("jllm_depth_mix", stack.data_ptr(), stack.stride(0), weights.data_ptr(), _DT[weights.dtype], int(n), out.data_ptr(),
           out.numel(), _stream())
+
+
+def norm_add_mix(x, a, gain, eps, stack, weights, n, mix_out, center: bool = True, shift=None, batch=None, h_out=None) -> None:
+    """`norm_add` and `depth_mix` in one launch: x += norm(a) * gain, where x is plane n - 1 of `stack`; mix_out = sum over
+    j < n of weights[j] * stack[j]. With `shift` = (mu, state) and a batch whose segments are one row each, also the next
+    layer's `token_shift`: h_out = mix + (state[slot] - mix) * mu and state[slot] = mix."""
+    assert x.dtype == a.dtype == stack.dtype == mix_out.dtype == torch.float32 and x.shape == a.shape == mix_out.shape
+    assert x.is_contiguous() and a.is_contiguous() and mix_out.is_contiguous() and stack.stride(1) == x.shape[1]
+    assert x.data_ptr() == stack[n - 1].data_ptr() and weights.numel() >= n
+    mu, state = shift if shift is not None else (None, None)
+    if shift is not None:
+        assert batch.decode_only and h_out.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous()
+    _call("jllm_norm_add_mix", x.data_ptr(), a.data_ptr(), gain.data_ptr(), _DT[gain.dtype], x.shape[0], x.shape[1], float(eps),
+          int(bool(center)), stack.data_ptr(), stack.stride(0), weights.data_ptr(), _DT[weights.dtype], int(n),
+          mix_out.data_ptr(), _p(mu), _DT[mu.dtype] if mu is not None else F32, _p(state),
+          state.shape[0] if state is not None else 0, batch.row_seg.data_ptr() if shift is not None else 0,
+          batch.state_slots.data_ptr() if shift is not None else 0, _p(h_out), _DT[h_out.dtype] if h_out is not None else F32,
+          _stream())
 
 
 def scale_values(x, s: float) -> None:

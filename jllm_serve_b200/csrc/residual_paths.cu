@@ -11,6 +11,9 @@
 //                    value is read and then written by one thread), else by `token_shift_save` behind it, because a
 //                    segment's first and last rows are then different blocks.
 //   depth_mix        out = sum_j a[j] * X_j over n planes of one stack (ascending j), X_j at stack + j * plane
+//   norm_add_mix     norm_add, depth_mix and (where every segment is one row) the NEXT layer's token_shift in one launch, a
+//                    block per row: x[r] += norm(a[r]) * w is the newest plane of the stack, the mix of all planes goes to the
+//                    plane behind it, and its blend with the next layer's saved row leaves in the compute type
 //   scale_values     x *= s
 //
 // All arithmetic is float32; a row's result depends on that row (and the one in front of it) alone.
@@ -179,6 +182,87 @@ depth_mix_kernel(const float* __restrict__ stack, size_t plane, VecRef weights, 
     }
 }
 
+// x: the rows of plane n - 1 of the stack (read and written); mix_out: the rows of the plane that takes the mix. With
+// `shift`: h_out[r] = mix + (saved - mix) * mu and saved = mix, for the one-row segment of row r (the next layer's state).
+template <typename Tout>
+__global__ void __launch_bounds__(256)
+norm_add_mix_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain, int dim, float eps, int center,
+                    const float* __restrict__ stack, size_t plane, VecRef weights, int n, float* __restrict__ mix_out, int shift,
+                    VecRef mu, float* __restrict__ state, int slots, const int* __restrict__ row_seg,
+                    const int* __restrict__ state_slots, Tout* __restrict__ h_out) {
+    __shared__ float scratch[33];
+    __shared__ float wj[MIX_MAX];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) wj[j] = weights[j];
+    const float* src = a + (size_t)r * dim;
+    float* xr = x + (size_t)r * dim;
+    float* mr = mix_out + (size_t)r * dim;
+    float mean, inv;
+    row_statistics(src, dim, eps, center, scratch, mean, inv);      // (its barriers also publish wj)
+    float* saved = nullptr;
+    if (shift) {
+        const int slot = state_slots[row_seg[r]];
+        if (!jllm_in_bounds(slot, slots, BOUNDS_SLOT)) return;
+        saved = state + (size_t)slot * dim;
+    }
+    Tout* hr = shift ? h_out + (size_t)r * dim : nullptr;
+    const float* lower = stack + (size_t)r * dim;
+    if (rows_vec4(src, xr, dim) && rows_vec4(mr, lower, dim) && (plane & 3) == 0 && (!shift || rows_vec4(saved, hr, dim))) {
+        for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            float4 o = *reinterpret_cast<const float4*>(xr + i);
+            o.x = __fadd_rn(o.x, __fmul_rn(__fmul_rn(v.x - mean, inv), gain[i]));
+            o.y = __fadd_rn(o.y, __fmul_rn(__fmul_rn(v.y - mean, inv), gain[i + 1]));
+            o.z = __fadd_rn(o.z, __fmul_rn(__fmul_rn(v.z - mean, inv), gain[i + 2]));
+            o.w = __fadd_rn(o.w, __fmul_rn(__fmul_rn(v.w - mean, inv), gain[i + 3]));
+            *reinterpret_cast<float4*>(xr + i) = o;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n - 1; ++j) {
+                const float4 p = *reinterpret_cast<const float4*>(lower + (size_t)j * plane + i);
+                acc.x = fmaf(wj[j], p.x, acc.x);
+                acc.y = fmaf(wj[j], p.y, acc.y);
+                acc.z = fmaf(wj[j], p.z, acc.z);
+                acc.w = fmaf(wj[j], p.w, acc.w);
+            }
+            acc.x = fmaf(wj[n - 1], o.x, acc.x);
+            acc.y = fmaf(wj[n - 1], o.y, acc.y);
+            acc.z = fmaf(wj[n - 1], o.z, acc.z);
+            acc.w = fmaf(wj[n - 1], o.w, acc.w);
+            *reinterpret_cast<float4*>(mr + i) = acc;
+            if (shift) {
+                const float4 p = *reinterpret_cast<const float4*>(saved + i);
+                const float y0 = __fadd_rn(acc.x, __fmul_rn(p.x - acc.x, mu[i])), y1 = __fadd_rn(acc.y, __fmul_rn(p.y - acc.y, mu[i + 1]));
+                const float y2 = __fadd_rn(acc.z, __fmul_rn(p.z - acc.z, mu[i + 2])), y3 = __fadd_rn(acc.w, __fmul_rn(p.w - acc.w, mu[i + 3]));
+                if constexpr (sizeof(Tout) == 4) {
+                    *reinterpret_cast<float4*>(hr + i) = make_float4(y0, y1, y2, y3);
+                } else {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                    uint2 q;
+                    q.x = *reinterpret_cast<uint32_t*>(&lo);
+                    q.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(hr + i) = q;
+                }
+                *reinterpret_cast<float4*>(saved + i) = acc;
+            }
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float o = __fadd_rn(xr[i], __fmul_rn(__fmul_rn(src[i] - mean, inv), gain[i]));
+        xr[i] = o;
+        float acc = 0.f;
+        for (int j = 0; j < n - 1; ++j) acc = fmaf(wj[j], lower[(size_t)j * plane + i], acc);
+        acc = fmaf(wj[n - 1], o, acc);
+        mr[i] = acc;
+        if (shift) {
+            hr[i] = from_float<Tout>(__fadd_rn(acc, __fmul_rn(saved[i] - acc, mu[i])));
+            saved[i] = acc;
+        }
+    }
+}
+
 __global__ void scale_values_kernel(float* __restrict__ x, float s, size_t count) {
     pdl_wait();
     pdl_trigger();
@@ -255,6 +339,28 @@ JLLM_EXPORT int jllm_depth_mix(const float* stack, long long plane, const void* 
         jllm_launch(depth_mix_kernel<1>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, stack, (size_t)plane, w, n, out,
                     (size_t)count);
     return jllm_check_launch("depth_mix");
+}
+
+// stack: n planes of [rows, dim] float32 (plane j at stack + j * plane), the last of them x; a float32 [rows, dim]; mix_out
+// float32 [rows, dim]. mu (or null: no shift): the next layer's shift vector, with its state [slots, dim], the batch's
+// row -> segment and segment -> slot tables (every segment one row) and h_out [rows, dim] of type out_dtype.
+JLLM_EXPORT int jllm_norm_add_mix(float* x, const float* a, const void* gain, int gain_dtype, int rows, int dim, float eps,
+                                  int center, const float* stack, long long plane, const void* weights, int weights_dtype, int n,
+                                  float* mix_out, const void* mu, int mu_dtype, float* state, int slots, const int* row_seg,
+                                  const int* state_slots, void* h_out, int out_dtype, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && n >= 1 && n <= MIX_MAX && plane >= 0, "norm_add_mix: rows=%d dim=%d n=%d", rows, dim, n);
+    JLLM_REQUIRE(mu == nullptr || (state != nullptr && slots > 0 && row_seg != nullptr && state_slots != nullptr && h_out != nullptr),
+                 "norm_add_mix: a shift needs its state, the batch's tables and an output");
+    if (rows == 0) return JLLM_OK;
+    const VecRef g{gain, gain_dtype}, w{weights, weights_dtype}, m{mu, mu_dtype};
+    const int shift = mu != nullptr;
+    if (out_dtype == JLLM_F32)
+        jllm_launch(norm_add_mix_kernel<float>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, g, dim, eps, center, stack,
+                    (size_t)plane, w, n, mix_out, shift, m, state, slots, row_seg, state_slots, (float*)h_out);
+    else
+        jllm_launch(norm_add_mix_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, g, dim, eps, center,
+                    stack, (size_t)plane, w, n, mix_out, shift, m, state, slots, row_seg, state_slots, (__nv_bfloat16*)h_out);
+    return jllm_check_launch("norm_add_mix");
 }
 
 JLLM_EXPORT int jllm_scale_values(float* x, float s, long long count, cudaStream_t stream) {

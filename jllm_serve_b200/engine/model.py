@@ -129,7 +129,7 @@ class DecoderModel:
     def forward(self, batch, cache, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the batch's rows through every scheduled layer; returns float32 logits [wanted rows, vocab]."""
         rows = batch.rows
-        schedule, normed = self.spec.schedule, False
+        schedule, normed, shifted = self.spec.schedule, False, False
         stack = None
         if self.depth_weights is not None:
             # plane 0: the embedded rows; plane j + 1: run j's result, made in place from the mix that run j was handed
@@ -154,9 +154,20 @@ class DecoderModel:
                 nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
                 gain = nxt.mixer_norm.gain if getattr(nxt, "chains_norms", False) and nxt.eps == block.eps else None
                 normed = block.forward(x, batch, self._run_cache(cache, i), normed=normed, next_gain=gain)
+            elif stack is not None and getattr(block, "mixes_depth", False):
+                # an arrangement whose last launch can also mix the planes (and, in a step of single rows, shift the tokens
+                # for the block that follows) is handed the stack and that block's shift vector and state
+                nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+                shift = None
+                if batch.decode_only and getattr(nxt, "mixes_depth", False) and nxt.shift is not None:
+                    shift = (nxt.shift, self._run_cache(cache, i + 1).block_states[0])
+                shifted = block.forward(x, batch, self._run_cache(cache, i), shifted=shifted,
+                                        tail=(stack, self.depth_weights[i], i + 2, stack[i + 2], shift))
+                x = stack[i + 2]
+                continue
             else:
                 block.forward(x, batch, self._run_cache(cache, i))
-                normed = False
+                normed = shifted = False
             if stack is not None:
                 ops.depth_mix(stack, self.depth_weights[i], i + 2, stack[i + 2])
                 x = stack[i + 2]

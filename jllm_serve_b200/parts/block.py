@@ -247,12 +247,28 @@ class PostNormBlock(Block):
             y.zero_()
         return y
 
-    def forward(self, x, batch, cache) -> None:
+    mixes_depth = True         # `forward` takes `shifted` and `tail` and says whether it made the next block's shifted input
+
+    def _last_norm(self, x, a, gain, batch, tail) -> bool:
+        """The layer's last norm and residual sum; with `tail` = (stack, weights, n, out, next_shift) also the depth mix
+        behind the layer, and, in a step of single rows, the token shift of the block that follows (`next_shift` = its (mu,
+        state)); says whether that block's input is made."""
+        if tail is None:
+            ops.norm_add(x, a, gain, self.eps, center=self.center)
+            return False
+        stack, weights, n, out, next_shift = tail
+        shift = next_shift if batch.decode_only else None
+        xb = self.rt.buffer("normed", self.dim)[:x.shape[0]]
+        ops.norm_add_mix(x, a, gain, self.eps, stack, weights, n, out, self.center, shift, batch, xb if shift is not None else None)
+        return shift is not None
+
+    def forward(self, x, batch, cache, shifted: bool = False, tail=None) -> bool:
         rows = x.shape[0]
         low = self.rt.dtype != torch.float32            # the parts read a copy of the stream in the compute type
         xb = self.rt.buffer("normed", self.dim)[:rows]
         if self.shift is not None:
-            ops.token_shift(x, self.shift, cache.block_states[0], batch, xb)
+            if not shifted:                             # (else the block in front made it with its last launch)
+                ops.token_shift(x, self.shift, cache.block_states[0], batch, xb)
             h = xb
         elif low:
             xb.copy_(x)
@@ -262,12 +278,11 @@ class PostNormBlock(Block):
         a = self._result(self.mixer, rows)
         self.mixer.forward(h, a, batch, cache)
         if self.feed_forward is None:
-            ops.norm_add(x, a, self.mixer_gain, self.eps, center=self.center)
-            return
+            return self._last_norm(x, a, self.mixer_gain, batch, tail)
         ops.norm_add(x, a, self.mixer_gain, self.eps, next_out=xb if low else None, center=self.center)
         y = self._result(self.feed_forward, rows)
         self.feed_forward.forward(xb if low else x, y, batch)
-        ops.norm_add(x, y, self.ffn_gain, self.eps, center=self.center)
+        return self._last_norm(x, y, self.ffn_gain, batch, tail)
 
 
 register_block("post_norm", PostNormBlock, replace=True)

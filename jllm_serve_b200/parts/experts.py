@@ -36,11 +36,23 @@ class RoutedExperts(FeedForward):
         E, ff = spec.experts, spec.hidden
         self.hidden = E * ff
         self.on_input = getattr(spec, "weight_on", "output") == "input"
-        self.shared = None
-        if getattr(spec, "shared", None) is not None:
-            self.shared = part_class("feed_forward", spec.shared.kind)(spec.shared, dim, tensors, prefix + "shared.", runtime)
-        gate = torch.cat([tensors.pop(f"{prefix}e{e}.gate") for e in range(E)], dim=0)
-        up = torch.cat([tensors.pop(f"{prefix}e{e}.up") for e in range(E)], dim=0)
+        self.shared, self.shared_ff, self.shared_limit = None, 0, 0.0
+        shared = getattr(spec, "shared", None)
+        gates = [tensors.pop(f"{prefix}e{e}.gate") for e in range(E)]
+        ups = [tensors.pop(f"{prefix}e{e}.up") for e in range(E)]
+        downs = [tensors.pop(f"{prefix}e{e}.down") for e in range(E)]
+        if shared is not None and self.on_input and shared.kind == "dense_glu" and shared.activation == spec.activation:
+            # a shared expert of the same kind of unit rides behind the routed ones in both products, as an expert that every
+            # row uses with weight 1 (and a limit and size of its own)
+            self.shared_ff, self.shared_limit = shared.hidden, float(shared.limit)
+            gates.append(tensors.pop(prefix + "shared." + shared.names[0]))
+            ups.append(tensors.pop(prefix + "shared." + shared.names[1]))
+            downs.append(tensors.pop(prefix + "shared." + shared.names[2]))
+        elif shared is not None:
+            self.shared = part_class("feed_forward", shared.kind)(shared, dim, tensors, prefix + "shared.", runtime)
+        self.hidden = E * ff + self.shared_ff
+        gate, up = torch.cat(gates, dim=0), torch.cat(ups, dim=0)
+        del gates, ups
         # (a weight in front of the gated unit rules out the product's own epilogue, which gates what it has summed)
         self.fused = gate.dtype == torch.bfloat16 and dim % 8 == 0 and self.hidden % 8 == 0 and not self.on_input
         if self.fused:      # blocks of 8 gate rows followed by their 8 up rows: the product's epilogue applies SwiGLU
@@ -50,7 +62,8 @@ class RoutedExperts(FeedForward):
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous())
         del gate, up
-        self.down = Linear(torch.cat([tensors.pop(f"{prefix}e{e}.down") for e in range(E)], dim=1).contiguous())
+        self.down = Linear(torch.cat(downs, dim=1).contiguous())
+        del downs
         self.router = tensors.pop(prefix + "router")
         self.correction = tensors.pop(prefix + "correction") if spec.correction else None
 
@@ -75,7 +88,7 @@ class RoutedExperts(FeedForward):
         if self.on_input:
             gate_up = self.rt.buffer("experts_gate_up", 2 * self.hidden)[:rows]
             self.gate_up.forward(xb, gate_up)
-            ops.glu_clamped(gate_up, weights, h, s.experts, s.hidden, s.limit)
+            ops.glu_clamped(gate_up, weights, h, s.experts, s.hidden, s.limit, self.shared_ff, self.shared_limit)
         else:
             if self.fused:
                 self.gate_up.forward(xb, h, swiglu=True)

@@ -153,9 +153,9 @@ class LatentAttention(Mixer):
             q = self.rt.buffer("latent_heads_q", H * (dk + rd))[:rows]
             q.copy_(proj[:, self.offsets["q"]:self.offsets["q"] + H * (dk + rd)])
         ql = self.rt.buffer("latent_queries", H * W)[:rows]
-        ops.gemm_heads(q, self.q_to_latent, ql, a_head=dk + rd, out_head=W)
-        if rd:
-            ops.rope_heads(q, dk + rd, dk, ql, W, R, H, rd, rope.cos, rope.sin, rope.rotary_dim, batch.positions)
+        # (one more block per row tile and head turns the head's rotated part and puts it behind its latent-space query)
+        ops.gemm_heads(q, self.q_to_latent, ql, a_head=dk + rd, out_head=W,
+                       rope=(rd, rope.cos, rope.sin, rope.rotary_dim, batch.positions) if rd else None)
         att = self.rt.buffer("latent_attended", H * W)[:rows]
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
         per = 16 if H > 16 and ops.attention_decode_fits(ql.dtype, 16, 1, W) else H
