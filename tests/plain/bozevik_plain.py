@@ -133,9 +133,15 @@ def glu(h, w, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[p + "down"].T
 
 
-def routed_experts(h, w, p, ff):
+def routed_experts(h, w, p, ff, gaps=None):
+    """`gaps`, if a list: gets one tensor [T], by how much the last chosen expert's router logit lies above the first one
+    left out (infinite where every expert is used)."""
     E, top = ff["router"]["experts"], ff["router"]["top"]
-    s = torch.sigmoid(h @ w[p + "router"].T)
+    z = h @ w[p + "router"].T
+    s = torch.sigmoid(z)
+    if gaps is not None:
+        ordered = z.sort(dim=1, descending=True).values
+        gaps.append(ordered[:, top - 1] - ordered[:, top] if top < E else torch.full((h.shape[0],), float("inf"), dtype=h.dtype))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in torch.topk(s[t], top).indices.tolist():
@@ -145,16 +151,17 @@ def routed_experts(h, w, p, ff):
     return out
 
 
-def feed_forward(h, w, p, ff):
+def feed_forward(h, w, p, ff, gaps=None):
     if ff["kind"] == "dense":
         return glu(h, w, p, float(ff["limit"]))
-    return routed_experts(h, w, p, ff)
+    return routed_experts(h, w, p, ff, gaps)
 
 
 # ---- the model ----------------------------------------------------------------------------------------------------
 
-def forward_plain(cfg, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and, if asked, what every layer hands on: [layers, T, width])."""
+def forward_plain(cfg, w, tokens, return_layers=False, gaps=None):
+    """Logits [T, vocab] of one whole sequence (and, if asked, what every layer hands on: [layers, T, width]). `gaps`, if a
+    list: gets the routers' margins, one tensor [T] per layer with routed experts (see `routed_experts`)."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     results = [x]
@@ -167,9 +174,23 @@ def forward_plain(cfg, w, tokens, return_layers=False):
         c, r = cached[i if mx.get("kv_from") is None else mx["kv_from"]]
         x = x + layer_norm(latent_attention(h, w, p + "mix.", mx, eps, c, r), w[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + layer_norm(feed_forward(x, w, p + "mlp.", layer["mlp"]), w[p + "norm2"], eps)
+            x = x + layer_norm(feed_forward(x, w, p + "mlp.", layer["mlp"], gaps), w[p + "norm2"], eps)
         results.append(x)
         x = sum(w[p + "dwa"][j] * results[j] for j in range(i + 2))
         handed.append(x)
-    logits = layer_norm(x, w["final.norm"], eps) @ w["embed"].T * float(cfg["logit_scale"])
+    logits = layer_norm(x, w["final.norm"], eps) @ w["embed"].T * float(cfg.get("logit_scale", 1.0))
     return (logits, torch.stack(handed)) if return_layers else logits
+
+
+def forward(cfg, w, tokens):
+    return forward_plain(cfg, w, tokens)
+
+
+def greedy_generate(cfg, w, prompt, n):
+    """n tokens by the largest logit, every step a whole forward pass over all tokens so far."""
+    tokens, out = list(prompt), []
+    for _ in range(n):
+        t = int(forward_plain(cfg, w, tokens)[-1].argmax())
+        out.append(t)
+        tokens.append(t)
+    return out

@@ -1,0 +1,679 @@
+"""Bozevik on the GPU against the plain implementation: every mechanism alone, then whole models through the step
+function under every way of cutting the same requests, then generation and the trace program."""
+import json
+import math
+import subprocess
+import sys
+from pathlib import Path
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from tests import traces
+from tests.bozevik_cases import BOZEVIK, bozevik_folder
+from tests.helpers import ARGMAX_SHARE, RMS_TOL, TOL
+from tests.plain import bozevik_plain as P
+from tests.tiny import random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def ops():
+    from jllm_serve_b200.csrc import ops as o
+    o.require_device()
+    return o
+
+
+def close(got, want, dtype, what, share=None):
+    tol = (share if share is not None else 2e-5 if dtype == torch.float32 else 1.6e-2) * float(want.abs().max())
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    diff = float((got.double().cpu() - want.double()).abs().max())
+    assert diff <= tol, f"{what}: largest difference {diff:.3e} exceeds {tol:.3e}"
+
+
+def step_tables(counts, slots):
+    """What a kernel reads of a batch: each row's segment, the segments' first rows and lengths, their state slots."""
+    starts = [sum(counts[:i]) for i in range(len(counts))]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    return SimpleNamespace(row_seg=i32([s for s, n in enumerate(counts) for _ in range(n)]), seg_start=i32(starts),
+                           seg_len=i32(counts), state_slots=i32(slots), decode_only=all(n == 1 for n in counts)), starts
+
+
+# ---- every mechanism alone ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dim, rows", [(40, 3), (333, 17), (4096, 2)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("center", [True, False])
+def test_layer_norm_of_chosen_rows(dim, rows, out_dtype, center):
+    g = torch.Generator().manual_seed(dim)
+    x = torch.randn(rows + 4, dim, generator=g) * 3 + 1.5            # a mean that is not zero: the variance is about it
+    gain = torch.randn(dim, generator=g).bfloat16()
+    index = torch.tensor([rows + 3 - r for r in range(rows)], dtype=torch.int32)
+    out = torch.empty(rows, dim, dtype=out_dtype, device=DEV)
+    ops().layernorm(x.to(DEV), gain.to(DEV), 3e-5, out, index.to(DEV), center=center)
+    picked = x.double()[index.long()]
+    want = P.layer_norm(picked, gain.double(), 3e-5) if center else P.rms(picked, 3e-5) * gain.double()
+    close(out, want, out_dtype, "layer norm")
+
+
+@pytest.mark.parametrize("dim, rows", [(72, 5), (320, 33), (2048, 3)])
+@pytest.mark.parametrize("next_dtype", [None, torch.float32, torch.bfloat16])
+def test_norm_of_a_parts_result_added_to_the_stream(dim, rows, next_dtype):
+    g = torch.Generator().manual_seed(dim + 1)
+    x, a = torch.randn(rows, dim, generator=g), torch.randn(rows, dim, generator=g) * 7 - 2
+    gain = torch.randn(dim, generator=g).bfloat16()
+    xd = x.to(DEV)
+    nxt = torch.empty(rows, dim, dtype=next_dtype, device=DEV) if next_dtype is not None else None
+    ops().norm_add(xd, a.to(DEV), gain.to(DEV), 1e-6, next_out=nxt)
+    want = x.double() + P.layer_norm(a.double(), gain.double(), 1e-6)
+    close(xd, want, torch.float32, "stream")
+    if nxt is not None:
+        close(nxt, want, next_dtype, "the stream in the compute type")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_token_shift_over_portions_single_rows_and_slots(out_dtype):
+    """Three requests in slots 2, 0 and 3 of five: one in portions of 1 + 20 + 2 + 14, one whole, one row by row. Every
+    portion's first row blends with the row its request's step before left; the other slots keep what they had."""
+    o_, dim = ops(), 88
+    g = torch.Generator().manual_seed(4)
+    lengths, slots = {"a": 37, "b": 9, "c": 5}, {"a": 2, "b": 0, "c": 3}
+    xs = {r: torch.randn(n, dim, generator=g) for r, n in lengths.items()}
+    mu = (torch.rand(dim, generator=g) * 1.4 - 0.2).bfloat16()
+    state = torch.full((5, dim), 7.0, device=DEV)
+    for s in slots.values():
+        state[s].zero_()
+    steps = [[("a", 1), ("b", 9)], [("a", 20), ("c", 1)], [("c", 1), ("a", 2)], [("a", 14), ("c", 1)], [("c", 1)], [("c", 1)]]
+    fed, got = {r: 0 for r in lengths}, {r: [] for r in lengths}
+    for step in steps:
+        x = torch.cat([xs[r][fed[r]:fed[r] + n] for r, n in step]).to(DEV)
+        batch, starts = step_tables([n for _, n in step], [slots[r] for r, _ in step])
+        out = torch.full((x.shape[0], dim), float("nan"), dtype=out_dtype, device=DEV)
+        o_.token_shift(x, mu.to(DEV), state, batch, out)
+        for (r, n), s in zip(step, starts):
+            got[r].append(out[s:s + n].float().cpu())
+            fed[r] += n
+    assert (state[1] == 7).all() and (state[4] == 7).all()
+    for r in lengths:
+        close(torch.cat(got[r]), P.token_shift(xs[r].double(), mu.double()), out_dtype, f"shifted rows of {r}")
+        assert torch.equal(state[slots[r]].cpu(), xs[r][-1]), f"the row {r} left for its next step"
+
+
+@pytest.mark.parametrize("planes, rows, dim", [(2, 7, 72), (5, 40, 320), (9, 3, 1000)])
+def test_depth_mix_alone_and_behind_the_last_norm(planes, rows, dim):
+    o_ = ops()
+    g = torch.Generator().manual_seed(planes)
+    room = rows + 5                                                  # the planes lie further apart than the rows in use
+    stack = torch.randn(planes + 1, room, dim, generator=g).to(DEV)
+    weights = (torch.randn(planes, generator=g)).bfloat16()
+    view = stack[:, :rows]
+    out = torch.empty(rows, dim, device=DEV)
+    o_.depth_mix(view, weights.to(DEV), planes, out)
+    want = sum(weights[j].double() * view[j].double().cpu() for j in range(planes))
+    close(out, want, torch.float32, "depth mix")
+    # the same behind a norm and a residual sum, into the plane that follows; then with the next layer's token shift
+    a = (torch.randn(rows, dim, generator=g) * 3).to(DEV)
+    gain = torch.randn(dim, generator=g).bfloat16()
+    x_new = view[planes - 1].double().cpu() + P.layer_norm(a.double().cpu(), gain.double(), 1e-5)
+    want = sum(weights[j].double() * (x_new if j == planes - 1 else view[j].double().cpu()) for j in range(planes))
+    before = view.clone()
+    o_.norm_add_mix(view[planes - 1], a, gain.to(DEV), 1e-5, view, weights.to(DEV), planes, view[planes])
+    close(view[planes - 1], x_new, torch.float32, "the layer's result")
+    close(view[planes], want, torch.float32, "what the layer hands on")
+    assert torch.equal(view[:planes - 1], before[:planes - 1])
+    for h_dtype in (torch.float32, torch.bfloat16):
+        view.copy_(before)
+        batch, _ = step_tables([1] * rows, list(range(rows, 0, -1)))
+        state = torch.randn(rows + 2, dim, generator=g).to(DEV)
+        kept = state.clone()
+        mu = torch.rand(dim, generator=g).bfloat16()
+        h = torch.empty(rows, dim, dtype=h_dtype, device=DEV)
+        o_.norm_add_mix(view[planes - 1], a, gain.to(DEV), 1e-5, view, weights.to(DEV), planes, view[planes],
+                        shift=(mu.to(DEV), state), batch=batch, h_out=h)
+        close(view[planes], want, torch.float32, "what the layer hands on (with the shift)")
+        prev = kept[batch.state_slots.long()].double().cpu()
+        close(h, want + (prev - want) * mu.double(), h_dtype, "the next layer's shifted rows")
+        close(state[batch.state_slots.long()], want, torch.float32, "the rows kept for the next step")
+        assert torch.equal(state[0], kept[0]) and torch.equal(state[rows + 1], kept[rows + 1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("q_rank, rank, rope_dim, rotary", [(24, 32, 8, 8), (20, 40, 12, 12), (80, 96, 32, 32), (0, 24, 6, 4)])
+def test_query_latent_norm_and_the_cached_row(dtype, q_rank, rank, rope_dim, rotary):
+    """cq = rms(src[q part]) * gain; the cached row [rms(src[latent part]) * gain, the shared key part turned by the row's
+    position], written where the row's slot says, other rows of the cache untouched."""
+    from jllm_serve_b200.config import RopeTableSpec
+    from jllm_serve_b200.parts import RotaryTable
+    o_ = ops()
+    g = torch.Generator().manual_seed(rank)
+    rows, base, eps = 19, 300.0, 2e-5
+    q_off, d_off = 0, -(-q_rank // 8) * 8
+    width = d_off + -(-(rank + rope_dim) // 8) * 8
+    src = torch.randn(rows, width, generator=g) * 2
+    q_gain, gain = torch.randn(max(q_rank, 1), generator=g).bfloat16(), torch.randn(rank, generator=g).bfloat16()
+    positions = torch.tensor([3 * r + (500 if r % 4 == 0 else 0) for r in range(rows)], dtype=torch.int32)
+    slots = torch.tensor([(7 * r + 3) % 64 for r in range(rows)], dtype=torch.int32)
+    table = RotaryTable(RopeTableSpec(rotary_dim=rotary, theta=base, pairing="interleaved"), 1024, torch.device(DEV))
+    cache = torch.full((4, 1, 16, rank + rope_dim), 5.0, dtype=dtype, device=DEV)
+    cq = torch.empty(rows, q_rank, dtype=dtype, device=DEV) if q_rank else None
+    o_.latent_prepare(src.to(DEV), q_off, q_rank, q_gain.to(DEV) if q_rank else None, cq, d_off, rank, rope_dim, gain.to(DEV),
+                      table.cos, table.sin, rotary, positions.to(DEV), slots.to(DEV), cache, eps)
+    s = src.double()
+    if q_rank:
+        close(cq, P.rms(s[:, :q_rank], eps) * q_gain.double(), dtype, "query latent")
+    flat = cache.view(-1, rank + rope_dim)
+    want_c = P.rms(s[:, d_off:d_off + rank], eps) * gain.double()
+    want_r = torch.stack([P.rotate_pairs(s[r:r + 1, d_off + rank:d_off + rank + rope_dim], [int(positions[r])], rotary, base)[0]
+                          for r in range(rows)])
+    close(flat[slots.long(), :rank], want_c, dtype, "cached latent")
+    close(flat[slots.long(), rank:], want_r, dtype, "cached rotated key part")
+    untouched = torch.ones(64, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert (flat[untouched.to(DEV)] == 5).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, K, N, rope_dim, rotary", [(3, 16, 32, 8, 8), (5, 12, 40, 12, 12), (20, 16, 96, 32, 32), (2, 24, 24, 6, 4)])
+def test_products_per_head_that_carry_the_rotated_part_along(dtype, heads, K, N, rope_dim, rotary):
+    """out[r, h] = [w[h] q[r, h, :K], rot(q[r, h, K:], position of r)]: a head's query in the latent's space."""
+    from jllm_serve_b200.config import RopeTableSpec
+    from jllm_serve_b200.parts import RotaryTable
+    o_ = ops()
+    g = torch.Generator().manual_seed(heads)
+    rows, base = 70, 1000.0
+    q = torch.randn(rows, heads * (K + rope_dim), generator=g).to(dtype)
+    w = torch.randn(heads, N, K, generator=g).to(dtype)
+    positions = torch.tensor([(11 * r) % 900 for r in range(rows)], dtype=torch.int32)
+    table = RotaryTable(RopeTableSpec(rotary_dim=rotary, theta=base, pairing="interleaved"), 1024, torch.device(DEV))
+    out = torch.full((rows, heads * (N + rope_dim)), float("nan"), dtype=dtype, device=DEV)
+    o_.gemm_heads(q.to(DEV), w.to(DEV), out, a_head=K + rope_dim, out_head=N + rope_dim,
+                  rope=(rope_dim, table.cos, table.sin, rotary, positions.to(DEV)))
+    qh = q.double().view(rows, heads, K + rope_dim)
+    want = torch.cat([torch.einsum("rhk,hnk->rhn", qh[:, :, :K], w.double()),
+                      P.rotate_pairs(qh[:, :, K:], positions.tolist(), rotary, base)], dim=2)
+    close(out, want.reshape(rows, -1), dtype, "latent-space queries")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts, ff, shared_ff", [(1, 40, 0), (4, 24, 16), (3, 10, 0), (16, 96, 128), (5, 7, 3)])
+def test_clamped_gated_unit_with_a_weight_on_the_input(dtype, experts, ff, shared_ff):
+    """g = min(w a, limit), u = clamp(w b, -limit, limit), out = g sigmoid(1.702 g) (u + 1): the limit cuts the gate from
+    above only; a weight of 0 gives exact zeros; the shared units have weight 1 and a limit of their own."""
+    o_ = ops()
+    g_ = torch.Generator().manual_seed(experts * 100 + ff)
+    rows, limit, shared_limit = 21, 1.25, 0.5
+    width = experts * ff + shared_ff
+    gate_up = (torch.randn(rows, 2 * width, generator=g_) * 3).to(dtype)
+    weights = torch.rand(rows, experts, generator=g_) * (torch.rand(rows, experts, generator=g_) < 0.5)
+    out = torch.full((rows, width), float("nan"), dtype=dtype, device=DEV)
+    o_.glu_clamped(gate_up.to(DEV), weights.to(DEV) if experts > 1 else None, out, experts, ff, limit, shared_ff, shared_limit)
+    a, b = gate_up.double()[:, :width], gate_up.double()[:, width:]
+    w = torch.ones(rows, width, dtype=torch.float64)
+    lim = torch.full((width,), limit, dtype=torch.float64)
+    if experts > 1:
+        w[:, :experts * ff] = weights.double().repeat_interleave(ff, dim=1)
+    lim[experts * ff:] = shared_limit
+    g = torch.minimum(w * a, lim)
+    u = torch.maximum(torch.minimum(w * b, lim), -lim)
+    close(out, g * torch.sigmoid(1.702 * g) * (u + 1), dtype, "clamped gated unit")
+    if experts > 1:
+        unused = (weights == 0).repeat_interleave(ff, dim=1)
+        assert (out.cpu()[:, :experts * ff][unused] == 0).all()
+    assert (a.min() < -limit) and (a.max() > limit)                    # (the inputs reach beyond the limits on both sides)
+
+
+@pytest.mark.parametrize("experts, top, dim", [(16, 1, 320), (4, 2, 64), (3, 3, 72), (6, 3, 128), (64, 6, 1000)])
+def test_router_weighs_by_the_plain_score_without_renormalizing(experts, top, dim):
+    g = torch.Generator().manual_seed(experts)
+    h = torch.randn(33, dim, generator=g)
+    router = torch.randn(experts, dim, generator=g) / math.sqrt(dim) * 2
+    got = torch.empty(33, experts, dtype=torch.float32, device=DEV)
+    ops().route_experts(h.to(DEV), router.to(DEV), None, top, 1.0, False, got)
+    s = torch.sigmoid(h.double() @ router.double().T)
+    want = torch.zeros_like(s)
+    idx = torch.topk(s, top, dim=1).indices
+    want.scatter_(1, idx, s.gather(1, idx))
+    assert ((got > 0).sum(dim=1) == top).all()
+    close(got, want, torch.float32, "router weights")
+
+
+def _runtime(dtype, max_rows=512, page=16, ctx=1024):
+    from jllm_serve_b200.parts import Runtime
+    ops()
+    return Runtime(torch.device(DEV), dtype, ctx, max_rows, page)
+
+
+def _part_weights(cls, spec, dim, prefix, dtype, seed, gains=None):
+    """Random bfloat16 values with unit gain per matrix (times `gains[suffix]`); (float64 on the CPU, the device's copies)."""
+    from jllm_serve_b200.weights import random_tensors
+    wants = cls.wants(spec, dim, prefix)
+    cpu = random_tensors(wants, seed, "cpu", torch.bfloat16)
+    for k, v in cpu.items():
+        if v.dim() == 2:
+            gain = next((f for suffix, f in (gains or {}).items() if k.endswith(suffix)), 1.0)
+            cpu[k] = (v.float() * (gain / (0.02 * v.shape[1] ** 0.5))).bfloat16()
+    dev = {k: v.to(DEV, torch.float32 if wants[k].role == "matrix_fp32" else dtype if wants[k].role == "matrix" else v.dtype)
+           for k, v in cpu.items()}
+    return {k: v.double() for k, v in cpu.items()}, dev
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim, hidden, limit, rows", [(80, 152, 1.0, 40), (72, 52, 2.5, 1), (256, 512, 0.75, 130), (64, 30, 1.5, 9)])
+def test_dense_feed_forward_with_the_clamped_unit(dtype, dim, hidden, limit, rows):
+    """Both forms: gate and up rows interleaved for the products' own epilogue (bfloat16, sizes in eights), and apart."""
+    from jllm_serve_b200.config import DenseGluSpec
+    from jllm_serve_b200.parts import DenseGlu
+    spec = DenseGluSpec(hidden=hidden, activation="swish_clamped", names=("gate", "up", "down"), limit=limit)
+    cpu, dev = _part_weights(DenseGlu, spec, dim, "f.", dtype, 5, gains={".gate": 2.0, ".up": 2.0})
+    ffn = DenseGlu(spec, dim, dev, "f.", _runtime(dtype))
+    xb = torch.randn(rows, dim).to(dtype)
+    for overwrite in (False, True):
+        ffn.overwrite = overwrite
+        x = torch.randn(rows, dim)
+        xd = x.to(DEV)
+        ffn.forward(xb.to(DEV), xd, None)
+        want = P.glu(xb.double(), cpu, "f.", limit) + (0 if overwrite else x.double())
+        close(xd, want, dtype, f"clamped feed-forward (overwrite={overwrite})", share=None if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts, top, ff, shared", [(4, 2, 24, (16, 1.5)), (16, 1, 96, (128, 0.5)), (3, 3, 10, None), (5, 1, 12, (7, 2.0))])
+def test_routed_experts_with_the_weight_on_the_input_and_a_shared_expert(dtype, experts, top, ff, shared):
+    from jllm_serve_b200.config import DenseGluSpec, RoutedExpertsSpec
+    from jllm_serve_b200.parts import RoutedExperts
+    dim, rows, limit = 72, 37, 1.25
+    shared_spec = DenseGluSpec(hidden=shared[0], activation="swish_clamped", names=("gate", "up", "down"), limit=shared[1]) if shared else None
+    spec = RoutedExpertsSpec(experts=experts, top=top, hidden=ff, scale=1.0, correction=False, normalize=False,
+                             activation="swish_clamped", limit=limit, weight_on="input", shared=shared_spec)
+    cpu, dev = _part_weights(RoutedExperts, spec, dim, "m.", dtype, 6, gains={".gate": 3.0, ".up": 3.0, "router": 2.0})
+    part = RoutedExperts(spec, dim, dev, "m.", _runtime(dtype))
+    part.overwrite = True
+    xb = torch.randn(rows, dim).to(dtype)
+    out = torch.full((rows, dim), float("nan"), device=DEV)
+    part.forward(xb.to(DEV), out, None)
+    ffd = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": limit},
+           "shared": {"ff": shared[0], "limit": shared[1]} if shared else None}
+    want = P.routed_experts(xb.double(), cpu, "m.", ffd)
+    # (a row whose choice hangs on less than rounding is no test of anything)
+    s = torch.sigmoid(xb.double() @ cpu["m.router"].T).sort(dim=1, descending=True).values
+    sure = torch.ones(rows, dtype=torch.bool) if top == experts else (s[:, top - 1] - s[:, top]) > 1e-4
+    assert sure.sum() >= rows - 2
+    close(out.cpu()[sure], want[sure], dtype, "routed experts", share=None if dtype == torch.float32 else 2.5e-2)
+    # the weight sits in front of the gated unit: with it behind, the result differs by far more than the tolerance
+    behind = torch.zeros_like(want)
+    sc = torch.sigmoid(xb.double() @ cpu["m.router"].T)
+    for t in range(rows):
+        for e in torch.topk(sc[t], top).indices.tolist():
+            behind[t] += sc[t, e] * P.glu(xb.double()[t:t + 1], cpu, f"m.e{e}.", limit)[0]
+    routed = want - (P.glu(xb.double(), cpu, "m.shared.", shared[1]) if shared else 0)
+    assert float((behind - routed).abs().max()) > 0.05 * float(routed.abs().max())
+
+
+def _mixer_cfg(heads, dk, dv, R, qr, rd, base, scale, source=None):
+    mx = {"heads": heads, "dim": dk, "vdim": dv, "kv_rank": R, "q_rank": qr, "rot_dim": rd, "rot": {"dims": rd, "base": base},
+          "scale": scale}
+    if source is not None:
+        mx["kv_from"] = source
+    return mx
+
+
+def _mixer_spec(mx, eps):
+    from jllm_serve_b200.config import LatentAttentionSpec
+    return LatentAttentionSpec(heads=mx["heads"], key_dim=mx["dim"], value_dim=mx["vdim"], rank=mx["kv_rank"], scale=mx["scale"],
+                               norm_eps=eps, gated=False, query_rank=mx["q_rank"], rope_dim=mx["rot_dim"], rope_table=0,
+                               own_latent="kv_from" not in mx)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("page", [16, 8])
+def test_latent_attention_finds_single_keys_far_back_first_and_at_page_borders(dtype, page):
+    """The mixer alone over a real cache manager and batch builder: one request of 400 rows fed in portions (150, 2, 228)
+    and then row by row beside a second request, and a second mixer with other heads that reads the first one's cached rows.
+    For chosen pairs (t, j) the input row j is made so that its latent points where head 0's query at t points: that
+    key then takes most of the weight, so a key that is lost, masked or read from the wrong page changes the whole row."""
+    from jllm_serve_b200.cache import CacheManager
+    from jllm_serve_b200.config import RopeTableSpec
+    from jllm_serve_b200.csrc import ops as o_
+    from jllm_serve_b200.engine.batch import BatchBuilder, Segment
+    from jllm_serve_b200.parts import LatentAttention, RotaryTable, RunCache
+    dim, eps, T, Tb = 64, 2e-5, 400, 40
+    own = _mixer_cfg(3, 16, 24, 32, 24, 8, 100.0, 0.3)
+    reader = _mixer_cfg(2, 8, 16, 32, 16, 8, 100.0, 0.45, source=0)
+    rt = _runtime(dtype, page=page)
+    cpu, dev = _part_weights(LatentAttention, _mixer_spec(own, eps), dim, "a.", dtype, 11, gains={".uq": 4.0})
+    cpu2, dev2 = _part_weights(LatentAttention, _mixer_spec(reader, eps), dim, "b.", dtype, 12, gains={".uq": 4.0})
+    rope = RotaryTable(RopeTableSpec(rotary_dim=8, theta=100.0, pairing="interleaved"), 1024, torch.device(DEV))
+    first = LatentAttention(_mixer_spec(own, eps), dim, dict(dev), "a.", rt, rope=rope)
+    second = LatentAttention(_mixer_spec(reader, eps), dim, dict(dev2), "b.", rt, rope=rope)
+
+    g = torch.Generator().manual_seed(13)
+    h = {"a": torch.randn(T, dim, generator=g).to(dtype).double(), "b": torch.randn(Tb, dim, generator=g).to(dtype).double()}
+    # (query row, key row): the first row from the last; the two sides of a page border from a prompt's portion and from
+    # single rows; the row just in front; a row 300 back; the first row of the portion of two
+    pairs = [(399, 0), (200, page - 1), (201, page), (390, 2 * page - 1), (391, 2 * page), (151, 150), (385, 85), (395, 394),
+             (152, 3 * page)]
+    R = own["kv_rank"]
+    down = cpu["a.dkv"][:R]
+    for t, j in pairs:
+        cq = P.rms(h["a"][t:t + 1] @ cpu["a.dq"].T, eps) * cpu["a.dq.norm"]
+        q0 = (cq @ cpu["a.uq"].T)[0, :own["dim"]]                                 # head 0, the part that is not rotated
+        target = (cpu["a.uk"][:own["dim"]].T @ q0) / cpu["a.dkv.norm"]
+        row = torch.linalg.pinv(down) @ target
+        h["a"][j] = (row * (dim ** 0.5 / row.norm())).to(dtype).double()
+    c, r = P.latent_of(h["a"], cpu, "a.", own, eps)
+    cb, rb = P.latent_of(h["b"], cpu, "a.", own, eps)
+    want = {"a": (P.latent_attention(h["a"], cpu, "a.", own, eps, c, r), P.latent_attention(h["a"], cpu2, "b.", reader, eps, c, r)),
+            "b": (P.latent_attention(h["b"], cpu, "a.", own, eps, cb, rb), P.latent_attention(h["b"], cpu2, "b.", reader, eps, cb, rb))}
+    # the pairs do what they are made for: head 0 at t gives row j nearly all of its weight
+    k0 = c @ cpu["a.uk"][:own["dim"]].T
+    for t, j in pairs:
+        cq = P.rms(h["a"][t:t + 1] @ cpu["a.dq"].T, eps) * cpu["a.dq.norm"]
+        q = (cq @ cpu["a.uq"].T)[0, :own["dim"] + own["rot_dim"]]
+        qr = P.rotate_pairs(q[None, own["dim"]:], [t], 8, 100.0)[0]
+        s = torch.softmax((k0[:t + 1] @ q[:own["dim"]] + r[:t + 1] @ qr) * own["scale"], dim=0)
+        assert float(s[j]) > 0.5, (t, j, float(s[j]))
+
+    def allocate(shape, kind):
+        return torch.full(shape, float("nan"), dtype=dtype, device=DEV)
+
+    pages = -(-T // page) + -(-Tb // page) + 1
+    cache = CacheManager([LatentAttention.cache_need(_mixer_spec(own, eps)), None], page, pages, 4, allocate=allocate)
+    builder = BatchBuilder(torch.device(DEV), 512, 4, -(-1024 // page), 1, page, o_.resident_blocks())
+    steps = [[("a", 150)], [("a", 2), ("b", 17)], [("b", 2), ("a", 228)]] + [[("a", 1), ("b", 1)]] * 20 + [[("b", 1)]]
+    fed, got = {"a": 0, "b": 0}, {"a": ([], []), "b": ([], [])}
+    for step in steps:
+        segs, rows = [], []
+        for rid, n in step:
+            if not cache.is_open(rid):
+                cache.open(rid)
+            cache.reserve(rid, fed[rid], n)
+            segs.append(Segment(rid, [0] * n, fed[rid]))
+            rows.append(h[rid][fed[rid]:fed[rid] + n])
+        batch = builder.build(segs, cache, 10)
+        xb = torch.cat(rows).to(DEV, dtype)
+        k, v = cache.keys_values(0)
+        for which, (mixer, writes) in enumerate(((first, True), (second, False))):
+            x = torch.zeros(xb.shape[0], dim, device=DEV)
+            mixer.forward(xb, x, batch, RunCache(0, writes, 0, k, v))
+            at = 0
+            for rid, n in step:
+                got[rid][which].append(x[at:at + n].cpu())
+                at += n
+        for rid, n in step:
+            fed[rid] += n
+            cache.commit(rid, fed[rid])
+    o_.check_kernel_errors()
+    assert fed == {"a": T, "b": Tb}
+    for rid in got:
+        for which, name in enumerate(("its own cached rows", "another mixer's cached rows")):
+            out = torch.cat(got[rid][which])
+            tol = (2e-5 if dtype == torch.float32 else 5e-2) * float(want[rid][which].abs().max())
+            diff = (out.double() - want[rid][which]).abs().amax(dim=1)
+            bad = (diff > tol).nonzero().flatten().tolist()
+            assert torch.isfinite(out).all() and not bad, f"{rid}, {name}: rows {bad[:8]} differ by up to {float(diff.max()):.3e} (> {tol:.3e})"
+
+
+# ---- whole models through the step function ---------------------------------------------------------------------------
+
+# bfloat16 rows against float64 ones, as a share of the largest |logit|: every part's result is normed to the stream's own
+# size before it is added, so a part's rounding reaches the logits undiminished (a stream that only grows would dilute it)
+BOZEVIK_TOL = {"float32": TOL["float32"], "bfloat16": 2.5e-2}
+CLOSE_CALL = 0.15      # a router logit margin below which bfloat16 rounding of the router's input may turn the choice
+
+
+class Comparison:
+    """Rows against the plain implementation's float64 logits. float32: every row within the tolerance. bfloat16: a
+    rounded input may turn a router's close call, which changes that token's experts outright and, through the attention
+    of the layers behind, every later row of its request. So in bfloat16 a row is held to the tolerance if no router
+    had a close call at or in front of it in its request (all rows, where every expert is used), the other rows have to be
+    finite; of the rows that are held, one in fifty may lie beyond the tolerance, none beyond twice it. The rms error and the share of equal choices hold over the rows that are held."""
+
+    def __init__(self, folder, sequences, dtype, what):
+        self.cfg, self.w = P.load_plain(folder)
+        self.sequences, self.dtype, self.what = sequences, dtype, what
+        self.plain, self.errors, self.flips, self.err2, self.ref2, self.scale = {}, [], 0, 0.0, 0.0, 0.0
+        self.seen, self.clean, self.loose = set(), {}, 0
+
+    def row(self, rid, position, got):
+        if rid not in self.plain:
+            gaps = []
+            self.plain[rid] = P.forward_plain(self.cfg, self.w, self.sequences[rid], gaps=gaps)
+            margin = torch.stack(gaps).amin(dim=0) if gaps else torch.full((len(self.sequences[rid]),), float("inf"))
+            close_calls = (margin < CLOSE_CALL).nonzero().flatten().tolist()
+            self.clean[rid] = close_calls[0] if close_calls and self.dtype != "float32" else len(self.sequences[rid])
+        want = self.plain[rid][position]
+        assert torch.isfinite(got).all(), f"{self.what}: non-finite logits for {rid} position {position}"
+        self.seen.add((rid, position))
+        if position >= self.clean[rid]:
+            self.loose += 1
+            return
+        d = got.double() - want
+        self.errors.append((float(d.abs().max()), rid, position))
+        self.err2 += float((d * d).sum())
+        self.ref2 += float((want * want).sum())
+        self.scale = max(self.scale, float(want.abs().max()))
+        self.flips += int(got.argmax()) != int(want.argmax())
+
+    def finish(self, least_held=0.0):
+        for rid, toks in self.sequences.items():
+            missing = [p for p in range(len(toks)) if (rid, p) not in self.seen]
+            assert not missing, f"{self.what}: no logits for {rid} positions {missing[:5]}"
+        assert len(self.errors) >= least_held * (len(self.errors) + self.loose) and self.errors
+        tol = BOZEVIK_TOL[self.dtype] * self.scale
+        worst = max(self.errors)
+        over = [e for e in self.errors if e[0] > tol]
+        rms = (self.err2 / max(self.ref2, 1e-300)) ** 0.5
+        print(f"{self.what} [{self.dtype}] rows held {len(self.errors)} (behind a close call: {self.loose}): largest difference "
+              f"{worst[0]:.3e} at {worst[1:]} ({worst[0] / self.scale:.2e} of the largest |logit|), {len(over)} rows over, rms {rms:.2e}")
+        first = min(over, key=lambda e: (e[1], e[2])) if over else None
+        # (bfloat16: one row in fifty may lie beyond the tolerance, none beyond twice it)
+        allowed = 0 if self.dtype == "float32" else max(1, len(self.errors) // 50)
+        assert len(over) <= allowed and worst[0] <= 2 * tol, \
+            f"{self.what}: {len(over)} rows beyond {tol:.3e}, the first at {first}, the largest {worst}"
+        assert rms <= 3 * RMS_TOL[self.dtype] and 1 - self.flips / len(self.errors) >= ARGMAX_SHARE[self.dtype] - 0.02
+
+
+def run_trace(name, dtype, steps, sequences, what, **kw):
+    from jllm_serve_b200.csrc import ops as o
+    from jllm_serve_b200.engine import ModelRunner, Segment
+    args = dict(dtype=dtype, page_size=16, max_tokens=traces.peak_tokens(steps, 16), max_batch_tokens=512, max_requests=4,
+                ctx=1024, poison_freed_pages=True)
+    args.update(kw)
+    runner = ModelRunner(bozevik_folder(name), **args)
+    compared = Comparison(bozevik_folder(name), sequences, dtype, f"{name} {what}")
+    fed = {}
+    for st in steps:
+        segs = [Segment(e["id"], e["tokens"], fed.get(e["id"], 0), e["want"]) for e in st["entries"]]
+        rows = runner.step(segs).float().cpu()
+        r = 0
+        for e in st["entries"]:
+            base = fed.get(e["id"], 0)
+            for w in e["want"]:
+                compared.row(e["id"], base + w, rows[r])
+                r += 1
+            fed[e["id"]] = base + len(e["tokens"])
+        for rid in st["end"]:
+            runner.finish(rid)
+            fed.pop(rid, None)
+    runner.cache.check()
+    o.check_kernel_errors()
+    compared.finish()
+    runner.close()
+
+
+def sequences_for(name, lengths, seed=21):
+    return {f"r{i}": random_tokens(n, BOZEVIK[name]["vocab"], seed + i) for i, n in enumerate(lengths)}
+
+
+LENGTHS = (1, 2, 37, 150, 16, 333, 65, 129)
+WAYS = {
+    "whole": traces.whole,
+    "prompt, then token by token": lambda r: traces.prompt_then_decode(r, tail=24),
+    "portions down to two tokens": traces.changing_portions,
+    "all requests side by side": lambda r: traces.all_together(dict(list(r.items())[:4]), tail=6),
+    "mixed, slots and pages used again": lambda r: traces.mixed(r, max_live=4, portion=40, prefill_share=0.7),
+}
+
+
+@pytest.mark.parametrize("way", list(WAYS))
+@pytest.mark.parametrize("name, dtype", [("P", "float32"), ("Q", "float32"), ("R", "float32"), ("Q", "bfloat16"), ("S", "bfloat16"),
+                                         ("R", "bfloat16")])
+def test_every_cut_of_the_same_requests_gives_the_plain_logits(name, dtype, way):
+    seqs = sequences_for(name, LENGTHS)
+    steps = WAYS[way](seqs)
+    used = {e["id"] for st in steps for e in st["entries"]}
+    run_trace(name, dtype, steps, {r: t for r, t in seqs.items() if r in used}, way)
+
+
+@pytest.mark.parametrize("name, dtype", [("P", "float32"), ("S", "bfloat16")])
+def test_the_layers_hand_on_what_the_plain_layers_hand_on(name, dtype):
+    """The weighted sum behind every layer, from the planes of the model's stack, for a prompt and for a step of single rows."""
+    from jllm_serve_b200.engine import ModelRunner, Segment
+    folder = bozevik_folder(name)
+    cfg, w = P.load_plain(folder)
+    toks = random_tokens(45, BOZEVIK[name]["vocab"], 77)
+    _, handed = P.forward_plain(cfg, w, toks, return_layers=True)
+    runner = ModelRunner(folder, dtype=dtype, page_size=16, max_tokens=64, max_batch_tokens=64, max_requests=2, ctx=64,
+                         cuda_graphs=False)
+    L, rt = len(cfg["layers"]), runner.runtime
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for lo, hi in ((0, 44), (44, 45)):
+        runner.step([Segment("a", toks[lo:hi], lo, [])])
+        stack = rt.buffer("depth_stack", cfg["width"], torch.float32, rows=(L + 2) * rt.max_rows).view(L + 2, rt.max_rows, -1)
+        planes = stack[:, :hi - lo].double().cpu()          # plane j: layer j - 1's result (0: the embedded rows); the last: the last mix
+        for i in range(L):
+            mix = sum(w[f"l{i}.dwa"][j] * planes[j] for j in range(i + 2))
+            close(mix, handed[i, lo:hi], torch.float32, f"behind layer {i}, rows {lo}..{hi}", share=tol)
+        close(planes[L + 1], handed[L - 1, lo:hi], torch.float32, f"what the last layer hands on, rows {lo}..{hi}", share=tol)
+    runner.close()
+
+
+@pytest.mark.parametrize("name, dtype", [("P", "float32"), ("S", "bfloat16")])
+def test_long_decoding_and_a_page_size_that_cuts_elsewhere(name, dtype):
+    seqs = sequences_for(name, (420,), seed=5)
+    run_trace(name, dtype, traces.prompt_then_decode(seqs, tail=300), seqs, "300 tokens one by one", page_size=8)
+
+
+def test_a_state_slot_and_pages_that_are_used_again_start_clean():
+    """One state slot and few pages: every request gets the slot (the row its token shift blends with) and the pages the one
+    before it left; a request's first token must blend with zeros, not with the last row of the request before."""
+    seqs = sequences_for("Q", (90, 3, 61, 1, 40), seed=8)
+    run_trace("Q", "float32", traces.whole(seqs), seqs, "one slot", max_requests=1, max_tokens=96)
+    run_trace("Q", "float32", traces.changing_portions(seqs, sizes=(2, 9, 2, 31)), seqs, "one slot, portions", max_requests=1,
+              max_tokens=96)
+
+
+def test_more_rows_than_a_batch_holds_run_as_several_batches():
+    seqs = sequences_for("P", (300, 77), seed=12)
+    run_trace("P", "float32", traces.all_together(seqs, tail=2), seqs, "a step in parts", max_batch_tokens=64)
+
+
+def test_captured_steps_of_single_rows_equal_launched_ones():
+    """A step of single rows replayed from a captured graph gives the rows that plain launches give, bit for bit."""
+    from jllm_serve_b200.engine import ModelRunner, Segment
+    seqs = sequences_for("R", (30, 9, 50), seed=40)
+    steps = traces.all_together(seqs, tail=12)
+    rows = {}
+    for graphs in (False, True):
+        runner = ModelRunner(bozevik_folder("R"), dtype="bfloat16", page_size=16, max_tokens=512,
+                             max_batch_tokens=128, max_requests=4, ctx=256, cuda_graphs=graphs)
+        fed, out = {}, []
+        for st in steps:
+            segs = [Segment(e["id"], e["tokens"], fed.get(e["id"], 0), e["want"]) for e in st["entries"]]
+            out.append(runner.step(segs).float().cpu())
+            for e in st["entries"]:
+                fed[e["id"]] = fed.get(e["id"], 0) + len(e["tokens"])
+        rows[graphs] = torch.cat(out)
+        runner.close()
+    assert torch.equal(rows[False], rows[True])
+
+
+# ---- generation and the trace program -----------------------------------------------------------------------------------
+
+def engine_for(name, dtype, **kw):
+    from jllm_serve_b200.engine import Engine
+    args = dict(dtype=dtype, page_size=8, max_tokens_cached=1024, max_batch_tokens=64, chunk=32, min_chunk=4, max_running=4,
+                ctx=256)
+    args.update(kw)
+    return Engine(bozevik_folder(name), **args)
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_greedy_generation_float32_equals_plain(name):
+    from jllm_serve_b200.sampling import SamplingParams
+    cfg, w = P.load_plain(bozevik_folder(name))
+    prompts = [random_tokens(n, BOZEVIK[name]["vocab"], 40 + n) for n in (5, 17, 41, 2, 33, 9)]
+    got = engine_for(name, "float32").generate(prompts, SamplingParams.greedy_params(12, ignore_eos=True))
+    for p, r in zip(prompts, got):
+        assert r.tokens == P.greedy_generate(cfg, w, p, 12) and r.finish_reason == "length"
+
+
+def test_greedy_generation_bfloat16_follows_plain():
+    from jllm_serve_b200.sampling import SamplingParams
+    cfg, w = P.load_plain(bozevik_folder("S"))
+    prompts = [random_tokens(n, BOZEVIK["S"]["vocab"], 60 + n) for n in (9, 40, 70)]
+    got = engine_for("S", "bfloat16").generate(prompts, SamplingParams.greedy_params(10, ignore_eos=True))
+    for p, r in zip(prompts, got):
+        logits = P.forward(cfg, w, p + r.tokens[:-1])
+        for i, t in enumerate(r.tokens):
+            row = logits[len(p) - 1 + i]
+            assert float(row.max() - row[t]) <= 2 * BOZEVIK_TOL["bfloat16"] * float(logits.abs().max()), (i, t)
+
+
+def test_generation_with_preemption_in_a_small_pool_equals_plain():
+    from jllm_serve_b200.sampling import SamplingParams
+    cfg, w = P.load_plain(bozevik_folder("P"))
+    prompts = [random_tokens(n, BOZEVIK["P"]["vocab"], 80 + n) for n in (60, 1, 33, 64, 100, 20)]
+    params = SamplingParams.greedy_params(16, ignore_eos=True)
+    got = engine_for("P", "float32", max_tokens_cached=200, max_batch_tokens=48).generate(prompts, params)
+    for i, (p, r) in enumerate(zip(prompts, got)):
+        assert r.tokens == P.greedy_generate(cfg, w, p, 16), f"request {i}"
+
+
+def test_command_line_run_and_bench_on_a_bozevik_model(tmp_path):
+    folder = bozevik_folder("Q")
+    prompt = random_tokens(11, BOZEVIK["Q"]["vocab"], 5)
+    cmd = [sys.executable, str(ROOT / "bin" / "jllm"), "run", "--model", str(folder), "--dtype", "fp32", "--temp", "0",
+           "--max-tokens", "7", "--ctx", "64", "--ignore-eos", "--tokens", ",".join(map(str, prompt))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    cfg, w = P.load_plain(folder)
+    assert [int(t) for t in proc.stdout.strip().split(",")] == P.greedy_generate(cfg, w, prompt, 7)
+    assert "11 prompt tok" in proc.stderr and "7 generated" in proc.stderr
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(BOZEVIK["P"]))
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "jllm"), "bench", "--random-weights", "3", "--model-config",
+                           str(cfg_file), "--ctx", "256", "--bench.prompt-tokens", "50", "--bench.max-tokens", "8",
+                           "--bench.rounds", "2"], capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.startswith("prefill 50 tok in") and "decode 8 tok in" in proc.stdout
+
+
+@pytest.mark.parametrize("name, dtype", [("P", "float32"), ("S", "bfloat16")])
+def test_trace_program_on_a_bozevik_folder(name, dtype, tmp_path):
+    seqs = sequences_for(name, (50, 7, 1, 90, 33), seed=30)
+    steps = traces.mixed(seqs, max_live=4, portion=24)
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(bozevik_folder(name)), "--dtype", dtype,
+                           "--out", str(tmp_path), "--max-tokens", str(traces.peak_tokens(steps)), "--poison"],
+                          input=text, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    import numpy as np
+    vocab = BOZEVIK[name]["vocab"]
+    compared = Comparison(bozevik_folder(name), seqs, dtype, "trace program")
+    fed = {}
+    for st in steps:
+        rows = torch.from_numpy(np.fromfile(tmp_path / f"{st['step']}.f32", dtype="<f4").reshape(-1, vocab))
+        r = 0
+        for e in st["entries"]:
+            base = fed.get(e["id"], 0)
+            for w in e["want"]:
+                compared.row(e["id"], base + w, rows[r])
+                r += 1
+            fed[e["id"]] = base + len(e["tokens"])
+    compared.finish()
