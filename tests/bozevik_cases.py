@@ -60,7 +60,16 @@ BOZEVIK_S = json.loads(json.dumps(BOZEVIK_P))
 BOZEVIK_S["layers"][1]["mlp"]["router"]["top"] = 4
 BOZEVIK_S["layers"][3]["mlp"]["router"]["top"] = 3
 
-BOZEVIK = {"P": BOZEVIK_P, "Q": BOZEVIK_Q, "R": BOZEVIK_R, "S": BOZEVIK_S}
+# T: a width that is no multiple of 8, odd feed-forward and head sizes, seven heads of four values, top 4 of 5
+BOZEVIK_T = {"architecture": "Bozevik", "width": 100, "vocab": 97, "logit_scale": 1.5, "norm": {"eps": 1e-5}, "layers": [
+    _layer(3, 10, 6, 20, 10, 4, 50.0, 0.3, _moe(2, 1, 30, 1.0, shared=(6, 2.0))),
+    _layer(1, 6, 10, 20, 14, 4, 50.0, 0.5, _dense(33, 1.5), kv_from=0),
+    _layer(7, 4, 2, 10, 6, 2, 7.0, 0.4, _moe(5, 4, 9, 3.0))]}
+# U: one layer, cached rows of nine values
+BOZEVIK_U = {"architecture": "Bozevik", "width": 36, "vocab": 50, "norm": {"eps": 1e-5}, "layers": [
+    _layer(2, 5, 3, 7, 5, 2, 50.0, 0.3, _dense(11, 1.0))]}
+
+BOZEVIK = {"P": BOZEVIK_P, "Q": BOZEVIK_Q, "R": BOZEVIK_R, "S": BOZEVIK_S, "T": BOZEVIK_T, "U": BOZEVIK_U}
 
 
 def sharpen(tensors: dict, config: dict) -> dict:

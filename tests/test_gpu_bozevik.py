@@ -521,7 +521,7 @@ WAYS = {
 
 @pytest.mark.parametrize("way", list(WAYS))
 @pytest.mark.parametrize("name, dtype", [("P", "float32"), ("Q", "float32"), ("R", "float32"), ("Q", "bfloat16"), ("S", "bfloat16"),
-                                         ("R", "bfloat16")])
+                                         ("R", "bfloat16"), ("T", "float32"), ("U", "bfloat16")])
 def test_every_cut_of_the_same_requests_gives_the_plain_logits(name, dtype, way):
     seqs = sequences_for(name, LENGTHS)
     steps = WAYS[way](seqs)
