@@ -58,7 +58,7 @@ class RopeTableSpec:
 @dataclass(frozen=True)
 class NormSpec:
     kind: str = "rmsnorm"                  # rmsnorm | dynamic_tanh (tanh(a x) * w + b: no statistics, eps unused) |
-                                           # layernorm ((x - mean) / sqrt(variance + eps) * w, no bias)
+                                           # layernorm ((x - m) / sqrt(v + eps) * g with m the mean and v the mean squared deviation, no bias)
     eps: float = 1e-6
     gain_name: str = "weight"              # rmsnorm: the gain is the tensor <the norm's name> + gain_name ("": the name itself)
 

@@ -355,8 +355,8 @@ def glu_clamped(gate_up, weights, out, experts, ff, limit, shared_ff: int = 0, s
 
 
 def layernorm(x, gain, eps, out, row_index=None, rows=None, center: bool = True, out_scale: float = 1.0) -> None:
-    """out[r] = (x[s] - mean) / sqrt(variance + eps) * gain * out_scale, s = row_index[r] or r (`center` False: x[s] /
-    sqrt(mean(x^2) + eps)); x float32 [*, dim]; out float32 or bfloat16."""
+    """out[r] = (x[s] - m) / sqrt(v + eps) * gain * out_scale, m the mean of row s and v its mean squared deviation from m,
+    s = row_index[r] or r (`center` False: x[s] / sqrt(mean(x^2) + eps)); x float32 [*, dim]; out float32 or bfloat16."""
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     n = (row_index.numel() if row_index is not None else x.shape[0]) if rows is None else rows
     _call("jllm_layernorm", x.data_ptr(), gain.data_ptr(), _DT[gain.dtype], out.data_ptr(), _DT[out.dtype], _p(row_index), n,

@@ -53,7 +53,7 @@ register_norm("dynamic_tanh", DynamicTanh, replace=True)
 
 
 class LayerNorm(Norm):
-    """y = (x - mean) / sqrt(variance + eps) * w, the variance being the mean of the squared deviations; a weight and no
+    """y = (x - m) / sqrt(v + eps) * g over a row, m its mean and v its mean squared deviation from m; a gain g and no
     bias. Float32 arithmetic; the output has the compute dtype. `out_scale` multiplies the result (1 unless a model sets it)."""
 
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):

@@ -2,7 +2,7 @@
 
 Bozevik is a small decoder-only design: an embedding, a list of layers, a final layer norm and the embedding again as
 the head (times a constant). A layer is one attention over a cached latent (queries through a latent of their own, one
-rotated key part shared by all heads) and optionally a feed-forward (dense, or routed experts with a shared expert),
+rotated key part that every head uses) and optionally a feed-forward (dense, or routed experts with a shared expert),
 each followed by a layer norm on its RESULT before the residual sum. The mixer reads a blend of its input with the
 previous token's input (token shift), and what goes from one layer to the next is a weighted sum of the embedding and
 of every layer's result so far (depth average). A layer may read an earlier layer's cached latent instead of making one.
