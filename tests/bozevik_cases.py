@@ -72,6 +72,51 @@ BOZEVIK_U = {"architecture": "Bozevik", "width": 36, "vocab": 50, "norm": {"eps"
 BOZEVIK = {"P": BOZEVIK_P, "Q": BOZEVIK_Q, "R": BOZEVIK_R, "S": BOZEVIK_S, "T": BOZEVIK_T, "U": BOZEVIK_U}
 
 
+def draw_bozevik(seed: int) -> dict:
+    """A configuration drawn at random: 2 to 6 layers; every layer's heads, head widths, latents, scale and feed-forward
+    (none, dense, or experts with any top from 1 to all, with or without a shared expert) its own; a layer reads, with
+    probability 0.4, the rows of an earlier layer that has a latent (any such layer, not only the one in front of it) and
+    then shares that layer's row and rotation; now and then more than 16 heads, a rotation over part of the rotated values,
+    or no logit scale."""
+    import random
+    rnd = random.Random(seed)
+    layers, owners = [], []
+    for i in range(rnd.randint(2, 6)):
+        source = rnd.choice(owners) if owners and rnd.random() < 0.4 else None
+        if source is None:
+            rot_dim = 2 * rnd.randint(1, 12)
+            dims = rot_dim if rnd.random() < 0.8 else 2 * rnd.randint(1, rot_dim // 2)
+            kv_rank, base = rnd.randint(5, 72), rnd.choice([10.0, 500.0, 10000.0, 1e6])
+            owners.append(i)
+        else:
+            m = layers[source]["mixer"]
+            rot_dim, dims, kv_rank, base = m["rot_dim"], m["rot"]["dims"], m["kv_rank"], m["rot"]["base"]
+        heads = rnd.randint(17, 20) if rnd.random() < 0.15 else rnd.randint(1, 9)
+        dim = rnd.randint(3, 40)
+        pick = rnd.random()
+        if pick < 0.15:
+            mlp = None
+        elif pick < 0.5:
+            mlp = _dense(rnd.randint(6, 90), rnd.choice([0.5, 1.0, 2.0, 7.0]))
+        else:
+            experts = rnd.randint(2, 9)
+            shared = (rnd.randint(4, 40), rnd.choice([0.75, 1.5, 3.0])) if rnd.random() < 0.6 else None
+            mlp = _moe(experts, rnd.randint(1, experts), rnd.randint(4, 40), rnd.choice([0.5, 1.0, 2.0]), shared)
+        layer = _layer(heads, dim, rnd.randint(2, 40), kv_rank, rnd.randint(4, 60), rot_dim, base,
+                       round(rnd.uniform(0.5, 1.5) / (dim + rot_dim) ** 0.5, 4), mlp, kv_from=source)
+        layer["mixer"]["rot"]["dims"] = dims
+        layers.append(layer)
+    cfg = {"architecture": "Bozevik", "width": rnd.choice([40, 52, 64, 72, 90, 128]), "vocab": rnd.randint(40, 400),
+           "norm": {"eps": rnd.choice([1e-6, 1e-5, 3e-4])}, "layers": layers}
+    if rnd.random() < 0.8:
+        cfg["logit_scale"] = rnd.choice([0.25, 2.0, 5.0])
+    return cfg
+
+
+DRAWN = tuple(f"D{k}" for k in range(10))
+BOZEVIK.update({name: draw_bozevik(1000 + k) for k, name in enumerate(DRAWN)})
+
+
 def sharpen(tensors: dict, config: dict) -> dict:
     """Random weights of N(0, 0.02) leave every attention nearly uniform, every gated unit far inside its limits and the
     token shift and the depth weights without effect; a lost key, a stale row or a limit on the wrong side would not show.

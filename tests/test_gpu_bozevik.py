@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from tests import traces
-from tests.bozevik_cases import BOZEVIK, bozevik_folder
+from tests.bozevik_cases import BOZEVIK, DRAWN, bozevik_folder
 from tests.helpers import ARGMAX_SHARE, RMS_TOL, TOL
 from tests.plain import bozevik_plain as P
 from tests.tiny import random_tokens
@@ -432,7 +432,8 @@ class Comparison:
     had a close call at or in front of it in its request (all rows, where every expert is used), the other rows have to be
     finite; of the rows that are held, one in fifty may lie beyond the tolerance, none beyond twice it. The rms error and the share of equal choices hold over the rows that are held."""
 
-    def __init__(self, folder, sequences, dtype, what):
+    def __init__(self, folder, sequences, dtype, what, widen=1.0):
+        self.widen = widen
         self.cfg, self.w = P.load_plain(folder)
         self.sequences, self.dtype, self.what = sequences, dtype, what
         self.plain, self.errors, self.flips, self.err2, self.ref2, self.scale = {}, [], 0, 0.0, 0.0, 0.0
@@ -463,7 +464,7 @@ class Comparison:
             missing = [p for p in range(len(toks)) if (rid, p) not in self.seen]
             assert not missing, f"{self.what}: no logits for {rid} positions {missing[:5]}"
         assert len(self.errors) >= least_held * (len(self.errors) + self.loose) and self.errors
-        tol = BOZEVIK_TOL[self.dtype] * self.scale
+        tol = BOZEVIK_TOL[self.dtype] * self.widen * self.scale
         worst = max(self.errors)
         over = [e for e in self.errors if e[0] > tol]
         rms = (self.err2 / max(self.ref2, 1e-300)) ** 0.5
@@ -474,17 +475,19 @@ class Comparison:
         allowed = 0 if self.dtype == "float32" else max(1, len(self.errors) // 50)
         assert len(over) <= allowed and worst[0] <= 2 * tol, \
             f"{self.what}: {len(over)} rows beyond {tol:.3e}, the first at {first}, the largest {worst}"
-        assert rms <= 3 * RMS_TOL[self.dtype] and 1 - self.flips / len(self.errors) >= ARGMAX_SHARE[self.dtype] - 0.02
+        # (the share of equal choices means something only over enough rows)
+        assert rms <= 3 * RMS_TOL[self.dtype] * self.widen
+        assert len(self.errors) < 100 or 1 - self.flips / len(self.errors) >= ARGMAX_SHARE[self.dtype] - 0.02
 
 
-def run_trace(name, dtype, steps, sequences, what, **kw):
+def run_trace(name, dtype, steps, sequences, what, widen=1.0, **kw):
     from jllm_serve_b200.csrc import ops as o
     from jllm_serve_b200.engine import ModelRunner, Segment
     args = dict(dtype=dtype, page_size=16, max_tokens=traces.peak_tokens(steps, 16), max_batch_tokens=512, max_requests=4,
                 ctx=1024, poison_freed_pages=True)
     args.update(kw)
     runner = ModelRunner(bozevik_folder(name), **args)
-    compared = Comparison(bozevik_folder(name), sequences, dtype, f"{name} {what}")
+    compared = Comparison(bozevik_folder(name), sequences, dtype, f"{name} {what}", widen)
     fed = {}
     for st in steps:
         segs = [Segment(e["id"], e["tokens"], fed.get(e["id"], 0), e["want"]) for e in st["entries"]]
@@ -527,6 +530,23 @@ def test_every_cut_of_the_same_requests_gives_the_plain_logits(name, dtype, way)
     steps = WAYS[way](seqs)
     used = {e["id"] for st in steps for e in st["entries"]}
     run_trace(name, dtype, steps, {r: t for r, t in seqs.items() if r in used}, way)
+
+
+@pytest.mark.parametrize("name", DRAWN)
+def test_configurations_drawn_at_random_mixed_steps_and_a_decoded_tail(name):
+    """Layer counts, heads, widths, latents, sources of borrowed rows, feed-forwards and constants drawn at random: mixed
+    steps with slots and pages used again, then a prompt and a tail token by token, in float32 against the plain logits; the
+    mixed steps once more in bfloat16 (rows in front of a router's close call are held, the rest finite). Float32 rows are
+    held to 2e-5 of the largest logit: with up to 20 sharp heads and a logit scale of 5 the float32 rounding of single rows
+    reaches 1.2e-5, where a lost key or a stale row shows as 1e-2 and more; the same model's bfloat16 rows reach 0.09 (scores
+    of 10 and more, rounded at 2^-9 in the query and in the cached row), so the drawn models' bfloat16 rows are held to 0.1,
+    which is there to see that the bfloat16 kernels take every drawn size, not to measure them."""
+    seqs = sequences_for(name, (1, 2, 41, 150, 17, 230), seed=60)
+    run_trace(name, "float32", traces.mixed(seqs, max_live=3, portion=33, prefill_share=0.6), seqs, "drawn, mixed", widen=4.0,
+              max_requests=3)
+    tail = dict(list(seqs.items())[3:5])
+    run_trace(name, "float32", traces.prompt_then_decode(tail, tail=20), tail, "drawn, tail", widen=4.0)
+    run_trace(name, "bfloat16", traces.mixed(seqs, max_live=4, portion=50, prefill_share=0.5), seqs, "drawn, mixed", widen=4.0)
 
 
 @pytest.mark.parametrize("name, dtype", [("P", "float32"), ("S", "bfloat16")])
