@@ -48,6 +48,8 @@ class PagedKeysValues(CacheNeed):
                                            # positions (pages of chunks that have passed are given back, as under a window)
     planes: int = 2                        # 2: keys and values; 1: one row per position that serves as both (a latent
                                            # from which a mixer makes its keys and values)
+    keep_first: int = 0                    # with a window: the request's first keep_first positions stay visible to every
+                                           # later row, and the pages that hold them are never given back
 
 
 @dataclass(frozen=True)
@@ -187,6 +189,8 @@ class CacheManager:
         if not self._ptr:
             native.check(1)
         for gi, g in enumerate(self.paged):
+            if g.need.keep_first:
+                native.check(L.jh_cache_keep_first(self._ptr, gi, int(g.need.keep_first)), self._names)
             g.pool = PoolView(L.jh_cache_pool(self._ptr, gi), self._names, num_pages, f"group{gi}")
             g.pool.num_pages = num_pages
         self.slots = PoolView(L.jh_cache_pool(self._ptr, -1), self._names, max_requests, "state slots")

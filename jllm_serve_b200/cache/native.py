@@ -34,7 +34,7 @@ def lib():
             "jh_pool_new": ([I, c_char_p], P), "jh_pool_delete": ([P], None), "jh_pool_alloc": ([P, LL, PI], I),
             "jh_pool_free": ([P, I, LL], I), "jh_pool_check": ([P], I), "jh_pool_num_free": ([P], I),
             "jh_pool_holder": ([P, I], LL), "jh_pool_stats": ([P, PLL, PLL], None),
-            "jh_cache_new": ([I, PI, I, I, I], P), "jh_cache_delete": ([P], None), "jh_cache_open": ([P, LL, PI], I),
+            "jh_cache_new": ([I, PI, I, I, I], P), "jh_cache_delete": ([P], None), "jh_cache_keep_first": ([P, I, I], I), "jh_cache_open": ([P, LL, PI], I),
             "jh_cache_close": ([P, LL], I), "jh_cache_is_open": ([P, LL], I), "jh_cache_num_requests": ([P], I),
             "jh_cache_request_ids": ([P, PLL, I], I), "jh_cache_request": ([P, LL, PI, PI, PLL, PI], I),
             "jh_cache_table": ([P, LL, I, PI, I], I), "jh_cache_pages_missing": ([P, LL, I, I, PI], I),

@@ -24,7 +24,8 @@ class ConfigError(ValueError):
 @dataclass(frozen=True)
 class RopeScaling:
     """How the inverse frequencies of a rotary table are stretched (Scaling.java:6-78)."""
-    kind: str = "none"                     # none | linear | yarn
+    kind: str = "none"                     # none | linear | yarn | banded (by wavelength L = 2 pi / f: f where L < original /
+                                           # high, f / factor where L > original / low, a blend in between)
     factor: float = 1.0
     original_max_positions: int = 0        # yarn: the trained length
     beta_fast: float = 32.0
@@ -33,6 +34,8 @@ class RopeScaling:
     mscale_all_dim: float = 0.0
     attention_factor: float = 0.0          # 0 = derive from factor
     truncate: bool = True
+    low: float = 1.0                       # banded: the band's edges, in turns of the original length
+    high: float = 4.0
 
 
 @dataclass(frozen=True)
@@ -83,6 +86,7 @@ class AttentionNames:
     q_norm: str = "q_norm.weight"
     k_norm: str = "k_norm.weight"
     gate: str = "gate.weight"
+    sink: str = "sink"
 
 
 @dataclass(frozen=True)
@@ -105,8 +109,11 @@ class GqaAttentionSpec(MixerSpec):
     value_dim: int = 0                     # width of a value head; 0 = head_dim
     chunk: int = 0                         # 0 = none; else position i sees j <= i only if i // chunk == j // chunk
     unit_qk: bool = False                  # q and k over their root mean square (eps qk_norm_eps), after the rotation
-    gate: str = "none"                     # none | head_sigmoid: head h's result times sigmoid(Wg x)[h]
+    gate: str = "none"                     # none | head_sigmoid: head h's result times sigmoid(Wg x)[h] | sigmoid: every value
+                                           # of the concatenated heads times sigmoid(Wg x) of its own (Wg has heads x value_dim rows)
     names: AttentionNames = AttentionNames()
+    keep_first: int = 0                    # with a window: the sequence's first keep_first positions stay visible to every row
+    sink: bool = False                     # a learned number per query head whose exponential joins the softmax's denominator
 
     def __post_init__(self):
         if self.heads <= 0:
@@ -122,8 +129,10 @@ class GqaAttentionSpec(MixerSpec):
             raise ConfigError(f"attention: value_dim={self.value_dim} and chunk={self.chunk} must not be negative")
         if self.chunk and self.window:
             raise ConfigError("attention: a window and a chunk mask together are not built")
-        if self.gate not in ("none", "head_sigmoid"):
-            raise ConfigError(f"attention: gate {self.gate!r} is not built (built: none, head_sigmoid)")
+        if self.gate not in ("none", "head_sigmoid", "sigmoid"):
+            raise ConfigError(f"attention: gate {self.gate!r} is not built (built: none, head_sigmoid, sigmoid)")
+        if self.keep_first < 0 or (self.keep_first and not self.window):
+            raise ConfigError(f"attention: keep_first={self.keep_first} must not be negative and needs a window")
 
     @property
     def v_dim(self) -> int:
@@ -185,22 +194,89 @@ class FixedDecayLinearAttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class SelectiveStateSpaceSpec(MixerSpec):
+    """A state space whose step size and inputs depend on the token, with one scalar decay per head (the "state space
+    duality" form). One input projection gives [z | x B C | dt] (inner = heads x head_dim; B and C: groups x state each); x,
+    B and C pass a causal convolution of `conv` taps per channel and silu; dt = softplus(dt + dt_bias); per head (B, C of
+    group h // (heads / groups)) S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t; y silu(z) is
+    RMS-normed in `norm_groups` equal parts with a gain over all of it, then projected. State per request: S [heads, state,
+    head_dim] and the convolution's last conv - 1 inputs, both float32."""
+    kind: str = field(default="selective_state_space", init=False)
+    heads: int = 0
+    head_dim: int = 0
+    state: int = 0
+    groups: int = 1
+    conv: int = 4
+    norm_groups: int = 1
+    norm_eps: float = 1e-6
+
+    def __post_init__(self):
+        for name in ("heads", "head_dim", "state", "groups", "conv", "norm_groups"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"state space: {name}={getattr(self, name)} must be positive")
+        if self.heads % self.groups:
+            raise ConfigError(f"state space: groups={self.groups} must divide heads={self.heads}")
+        if (self.heads * self.head_dim) % self.norm_groups:
+            raise ConfigError(f"state space: norm_groups={self.norm_groups} must divide heads x vdim={self.heads * self.head_dim}")
+        if self.conv > 16:
+            raise ConfigError(f"state space: conv={self.conv} taps (built: up to 16)")
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(MixerSpec):
+    """A matrix memory with exponential gates: q = Wq h key_dim^(-1/2), k = Wk h, v = Wv h; per head a log input gate i = cap
+    tanh((Wi h + bi) / cap) and a log forget gate f = logsigmoid(cap tanh((Wf h + bf) / cap)); with a running maximum m (0 at
+    the start) m_t = max(f + m_(t-1), i): S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T, n_t the same with k alone,
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6); each head's o over its root mean square, a gain over all heads, a
+    sigmoid gate of full width, the output projection. State per request: S, n and m, float32."""
+    kind: str = field(default="matrix_memory", init=False)
+    heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+
+    def __post_init__(self):
+        for name in ("heads", "key_dim", "value_dim"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"matrix memory: {name}={getattr(self, name)} must be positive")
+        if not self.gate_cap > 0:
+            raise ConfigError(f"matrix memory: gate_cap={self.gate_cap} must be positive")
+        if self.key_dim > 512:
+            raise ConfigError(f"matrix memory: dim={self.key_dim} (built: up to 512)")
+
+
+@dataclass(frozen=True)
 class ParallelMixersSpec(MixerSpec):
     """Several mixers side by side on the same input; the result is `weight` times the sum of their results, each first
     RMS-normed over the model width with a gain of its own (`out_norms[i]`, relative to the mixer's prefix). Branch i's
-    tensors lie under `prefixes[i]`; each keeps its own cache or state."""
+    tensors lie under `prefixes[i]`; each keeps its own cache or state. With `weights` (one per branch) and no norms
+    (`out_norms` all ""): the result is the sum of weights[i] times branch i's result as it is."""
     kind: str = field(default="parallel_mixers", init=False)
     branches: Tuple[MixerSpec, ...] = ()
     prefixes: Tuple[str, ...] = ()
     out_norms: Tuple[str, ...] = ()
     norm_eps: float = 1e-6
     weight: float = 0.5
+    weights: Tuple[float, ...] = ()
 
     def __post_init__(self):
         if not 1 <= len(self.branches) <= 2:
             raise ConfigError(f"parallel mixers: {len(self.branches)} branches (built: one or two)")
         if not len(self.branches) == len(self.prefixes) == len(self.out_norms):
             raise ConfigError("parallel mixers: every branch needs a prefix and the name of its norm")
+        if self.weights and (len(self.weights) != len(self.branches) or any(self.out_norms)):
+            raise ConfigError("parallel mixers: weights per branch go with branches that are not normed, one weight each")
+        if not self.weights and not all(self.out_norms):
+            raise ConfigError("parallel mixers: branches without norms need a weight each")
 
     @property
     def rope_tables(self) -> tuple:
@@ -271,11 +347,29 @@ class DenseGluSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class DenseMlpSpec(FeedForwardSpec):
+    """down(act(up x)): two matrices and no gate."""
+    kind: str = field(default="dense_mlp", init=False)
+    hidden: int = 0
+    activation: str = "gelu_erf"           # gelu_erf: z (1 + erf(z / sqrt 2)) / 2
+    names: Tuple[str, str] = ("up", "down")
+
+    def __post_init__(self):
+        if self.hidden <= 0:
+            raise ConfigError(f"feed-forward: ff={self.hidden} must be positive")
+        if self.activation not in ("gelu_erf",):
+            raise ConfigError(f"unsupported activation {self.activation!r} of an ungated feed-forward (built: gelu_erf)")
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec(FeedForwardSpec):
     """`experts` gated feed-forwards of `hidden` units, of which a token uses `top`: scores s = sigmoid(Wr h); the `top`
     largest of s + correction are chosen (if `correction`); the weights are the chosen s over their sum (+ 1e-20, if
     `normalize`), times `scale`. `weight_on` "output": y = sum_e w_e expert_e(h); "input": y = sum_e expert_e(w_e h).
-    `shared`: a dense gated feed-forward (tensors under `shared.`) that every token runs, added to the experts' sum."""
+    `shared`: a dense gated feed-forward (tensors under `shared.`) that every token runs, added to the experts' sum; with
+    `shared_gate` (the name, under the feed-forward's prefix, of a [1, dim] matrix Wsg) it is first multiplied by sigmoid(Wsg h),
+    one number per token. `score` "softmax": s = softmax(Wr h) over all of the router's entries. `identity`: the router has
+    that many entries more than there are experts; one of them, when chosen, gives the token's input itself times its weight."""
     kind: str = field(default="routed_experts", init=False)
     experts: int = 0
     top: int = 0
@@ -287,12 +381,22 @@ class RoutedExpertsSpec(FeedForwardSpec):
     limit: float = 0.0
     weight_on: str = "output"              # output | input
     shared: Optional["DenseGluSpec"] = None
+    score: str = "sigmoid"                 # sigmoid | softmax
+    identity: int = 0
+    shared_gate: str = ""
 
     def __post_init__(self):
         if self.experts <= 0 or self.hidden <= 0:
             raise ConfigError(f"routed experts: experts={self.experts} and ff={self.hidden} must be positive")
-        if not 1 <= self.top <= self.experts:
-            raise ConfigError(f"routed experts: top={self.top} must lie in [1, experts={self.experts}]")
+        if self.identity < 0 or self.score not in ("sigmoid", "softmax"):
+            raise ConfigError(f"routed experts: identity={self.identity} score={self.score!r} (built: sigmoid, softmax)")
+        if not 1 <= self.top <= self.experts + self.identity:
+            raise ConfigError(f"routed experts: top={self.top} must lie in [1, experts={self.experts}"
+                              + (f" + identity={self.identity}]" if self.identity else "]"))
+        if (self.identity or self.shared_gate) and self.weight_on != "output":
+            raise ConfigError("routed experts: identity entries and a gate on the shared expert are built for weights on the output")
+        if self.shared_gate and self.shared is None:
+            raise ConfigError("routed experts: a gate on the shared expert needs a shared expert")
         if self.activation not in ("silu", "swish_clamped"):
             raise ConfigError(f"unsupported expert activation {self.activation!r}: silu and swish_clamped are built")
         if self.activation == "swish_clamped" and not self.limit > 0:
@@ -333,6 +437,7 @@ class LayerSpec:
     arrangement: str = "pre_norm"          # x += s * mixer(norm(x)); x += s * ffn(norm(x)), s = residual_scale
                                            # sandwich_norm: x += post(mixer(norm(x))); x += post'(ffn(norm'(x)))
                                            # post_norm: x += norm(mixer(x)); x += norm'(ffn(x)): the parts read x itself
+                                           # parallel_residual: h = norm(x); x += mixer(h) + ffn(h): one norm feeds both parts
     names: LayerNames = LayerNames()
     residual_scale: float = 1.0
     prefix: Optional[str] = None           # the layer's checkpoint prefix where it is not ModelNames.layer.format(index)
@@ -363,6 +468,7 @@ class Core:
     max_positions: int
     description: str = ""
     logit_scale: float = 1.0               # the head's result is multiplied by it
+    embedding_scale: float = 1.0           # the embedded rows are multiplied by it
 
 
 @dataclass(frozen=True)

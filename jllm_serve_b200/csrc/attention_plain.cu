@@ -8,6 +8,11 @@
 // the values, both in ascending key order. A row's result therefore depends on its own query and
 // keys only: not on how the prompt was cut, not on the other rows of the batch, not on the pages.
 //
+// Two things a mixer may add. `keep_first` > 0 (with a window): the request's first keep_first keys stay visible to every
+// later row, so a row sees [0, keep_first) and [first, P]; the keys in between are passed over. `sink` (one number per query
+// head, else null): the softmax's denominator also holds exp(sink[h]), a key without a value that is not multiplied by the
+// scale; the running maximum starts from it, so nothing overflows whichever is larger.
+//
 // Layouts: q [rows, q_stride] with head h at h * head_dim; cache K and V
 // [pages, kv_heads, page_size, cache_dim], a key in the first head_dim values of its row and a value in the first
 // value_dim; out [rows, out_stride] with head h at h * value_dim; block_tables [segments, table_stride]
@@ -25,7 +30,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const T* __restrict__ v_cache, T* __restrict__ out, int out_stride,
                        const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                        const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int head_dim,
-                       int value_dim, int cache_dim, int page_size, int num_pages, int window, float scale) {
+                       int value_dim, int cache_dim, int page_size, int num_pages, int window, float scale, int keep_first,
+                       VecRef sink, int has_sink) {
     extern __shared__ float smem[];
     float* qs = smem;                  // head_dim
     float* es = qs + head_dim;         // THREADS
@@ -34,6 +40,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     const int kvh = h / (heads / kv_heads);
     const int P = row_pos[r];
     const int first = jllm_first_key(P, window);
+    const int kept = window > 0 ? min(keep_first, first) : 0;      // keys [0, kept) in front of the window
     const int* table = block_tables + (size_t)row_seg[r] * table_stride;
     const T* qrow = q + (size_t)r * q_stride + (size_t)h * head_dim;
     for (int i = tid; i < head_dim; i += THREADS) qs[i] = to_float(qrow[i]);
@@ -52,22 +59,25 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
         return __fmul_rn(acc, scale);
     };
 
-    float m = -INFINITY;
-    for (int s = first + tid; s <= P; s += THREADS) m = fmaxf(m, score_of(s));
+    // the visible keys in ascending order: index u < kept is key u, index u >= kept is key first + (u - kept)
+    const int visible = kept + (P + 1 - first);
+    auto key_at = [&](int u) -> int { return u < kept ? u : first + (u - kept); };
+    float m = has_sink ? sink[h] : -INFINITY;
+    for (int u = tid; u < visible; u += THREADS) m = fmaxf(m, score_of(key_at(u)));
     m = block_max(m, scratch);
 
     float acc[MAX_DIMS_PER_THREAD] = {};
-    float sum = 0.f;
-    for (int s0 = first; s0 <= P; s0 += THREADS) {
-        const int s = s0 + tid;
+    float sum = has_sink ? expf(sink[h] - m) : 0.f;
+    for (int u0 = 0; u0 < visible; u0 += THREADS) {
+        const int u = u0 + tid;
         __syncthreads();
-        es[tid] = s <= P ? expf(score_of(s) - m) : 0.f;
+        es[tid] = u < visible ? expf(score_of(key_at(u)) - m) : 0.f;
         __syncthreads();
-        const int n = min(THREADS, P + 1 - s0);
+        const int n = min(THREADS, visible - u0);
         for (int j = 0; j < n; ++j) {
             const float e = es[j];
             sum += e;
-            const T* vr = key_row(v_cache, s0 + j);
+            const T* vr = key_row(v_cache, key_at(u0 + j));
             if (kCheckBounds && vr == nullptr) continue;
 #pragma unroll
             for (int c = 0; c < MAX_DIMS_PER_THREAD; ++c) {
@@ -92,7 +102,8 @@ JLLM_BOUNDS_READER(attention_plain)
 JLLM_EXPORT int jllm_attention_plain(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                      int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
                                      int table_stride, int rows, int heads, int kv_heads, int head_dim, int value_dim,
-                                     int cache_dim, int page_size, int window, float scale, int dtype, cudaStream_t stream) {
+                                     int cache_dim, int page_size, int window, float scale, int dtype, int keep_first,
+                                     const void* sink, int sink_dtype, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && head_dim > 0 && page_size > 0,
                  "attention: rows=%d heads=%d kv_heads=%d head_dim=%d page_size=%d", rows, heads, kv_heads, head_dim,
                  page_size);
@@ -101,6 +112,10 @@ JLLM_EXPORT int jllm_attention_plain(const void* q, int q_stride, const void* k_
     JLLM_REQUIRE(cache_dim >= head_dim && cache_dim >= value_dim, "attention: cache rows of %d values hold no key of %d or value of %d",
                  cache_dim, head_dim, value_dim);
     JLLM_REQUIRE(heads <= 65535, "attention: heads=%d", heads);
+    JLLM_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention: keep_first=%d needs a window (window=%d)",
+                 keep_first, window);
+    const VecRef sk{sink, sink_dtype};
+    const int has_sink = sink != nullptr;
     if (rows == 0) return JLLM_OK;
     const dim3 grid(rows, heads);
     const int num_pages = jllm_pool_pages();
@@ -108,11 +123,12 @@ JLLM_EXPORT int jllm_attention_plain(const void* q, int q_stride, const void* k_
     if (dtype == JLLM_F32)
         attention_plain_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, (float*)out, out_stride, row_seg,
-            row_pos, block_tables, table_stride, heads, kv_heads, head_dim, value_dim, cache_dim, page_size, num_pages, window, scale);
+            row_pos, block_tables, table_stride, heads, kv_heads, head_dim, value_dim, cache_dim, page_size, num_pages, window, scale,
+            keep_first, sk, has_sink);
     else
         attention_plain_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, head_dim,
-            value_dim, cache_dim, page_size, num_pages, window, scale);
+            value_dim, cache_dim, page_size, num_pages, window, scale, keep_first, sk, has_sink);
     return jllm_check_launch("attention_plain");
 }

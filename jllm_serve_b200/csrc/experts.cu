@@ -6,6 +6,12 @@
 // [rows, experts] float32 table: the feed-forward runs the experts as ONE product over their stacked gate / up rows
 // and ONE over their down matrices laid side by side along k, and a row's hidden values of expert e are multiplied by
 // its weight in between (`scale_expert_hidden`), so that experts a row does not use add exactly nothing.
+//
+// What a design may ask of the router beyond that: scores that are a softmax over all entries instead of a logistic function
+// of each (`softmax`); entries behind the experts that have no weights and hand the row through as it is (`identity`: the
+// router matrix has experts + identity rows, the chosen identity entries' weights leave as ONE number, their sum, in the
+// column behind the experts' and the gates'); and rows behind those that are not routed at all but give a logistic gate per
+// row (`gates`: a shared expert's), which leave in the columns behind the experts'.
 #include "common.cuh"
 
 namespace {
@@ -13,7 +19,11 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
 route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, VecRef correction, int has_correction,
-                     float* __restrict__ weights, int dim, int experts, int top, float scale, int normalize) {
+                     float* __restrict__ weights, int dim, int real, int top, float scale, int normalize, int identity, int gates,
+                     int softmax, int ld_out) {
+    // `real` experts have weights; entries [real, real + identity) hand the row through; rows [entries, entries + gates) of the
+    // router matrix are gates. `experts` below counts every row of the matrix.
+    const int entries = real + identity, experts = entries + gates;
     extern __shared__ float smem[];
     float* s = smem;                   // [experts] scores
     float* c = s + (experts + 1) / 2 * 2;      // [experts] choice scores, -inf once taken
@@ -53,54 +63,70 @@ route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ 
         }
         acc = warp_sum(acc);
         if (lane == 0) {
-            const float sc = 1.f / (1.f + expf(-acc));
+            const float sc = (softmax && e < entries) ? acc : 1.f / (1.f + expf(-acc));
             s[e] = sc;
-            c[e] = has_correction ? sc + correction[e] : sc;
+            c[e] = (has_correction && e < entries) ? sc + correction[e] : sc;
         }
     }
     __syncthreads();
-    float* out = weights + (size_t)r * experts;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) out[e] = 0.f;
+    float* out = weights + (size_t)r * ld_out;
+    for (int e = threadIdx.x; e < ld_out; e += blockDim.x) out[e] = 0.f;
     __syncthreads();
     if (threadIdx.x == 0) {
-        float sum = 0.f;
+        if (softmax) {                 // the logits become scores: exp(z - max) over their sum, in entry order
+            float top_z = -INFINITY, total = 0.f;
+            for (int e = 0; e < entries; ++e) top_z = fmaxf(top_z, s[e]);
+            for (int e = 0; e < entries; ++e) {
+                s[e] = expf(s[e] - top_z);
+                total += s[e];
+            }
+            for (int e = 0; e < entries; ++e) {
+                s[e] = s[e] / total;
+                c[e] = has_correction ? s[e] + correction[e] : s[e];
+            }
+        }
+        float sum = 0.f, through = 0.f;
         for (int k = 0; k < top; ++k) {
             int best = 0;
             float bv = -INFINITY;
-            for (int e = 0; e < experts; ++e)
+            for (int e = 0; e < entries; ++e)
                 if (c[e] > bv) { bv = c[e]; best = e; }
             c[best] = -INFINITY;
-            out[best] = s[best];
+            if (best < real) out[best] = s[best];
+            else through += s[best];
             sum += s[best];
         }
         const float f = normalize ? scale / (sum + 1e-20f) : scale;
-        for (int e = 0; e < experts; ++e) out[e] = __fmul_rn(out[e], f);
+        for (int e = 0; e < real; ++e) out[e] = __fmul_rn(out[e], f);
+        for (int g = 0; g < gates; ++g) out[real + g] = __fmul_rn(s[entries + g], scale);
+        if (identity) out[real + gates] = __fmul_rn(through, f);
     }
 }
 
 template <typename T>
 __global__ void scale_expert_hidden_kernel(T* __restrict__ hidden, const float* __restrict__ weights, int experts, int ff,
-                                           size_t total) {
+                                           size_t total, int ld_w, int shared_ff) {
+    // behind the experts' values may lie `shared_ff` values of one more unit, whose weight is column `experts` of the table
     pdl_wait();
     pdl_trigger();
-    const size_t width = (size_t)experts * ff;
+    const size_t routed = (size_t)experts * ff, width = routed + shared_ff;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / width, col = i - r * width;
-        hidden[i] = from_float<T>(__fmul_rn(to_float(hidden[i]), weights[r * experts + col / ff]));
+        hidden[i] = from_float<T>(__fmul_rn(to_float(hidden[i]), weights[r * ld_w + (col < routed ? col / ff : experts)]));
     }
 }
 
 // The same, 16 bytes a thread (ff a multiple of the 16-byte group: a group lies inside one expert).
 template <typename T>
 __global__ void scale_expert_hidden_vec_kernel(T* __restrict__ hidden, const float* __restrict__ weights, int experts, int ff,
-                                               size_t groups) {
+                                               size_t groups, int ld_w, int shared_ff) {
     constexpr int N = 16 / sizeof(T);
     pdl_wait();
     pdl_trigger();
-    const size_t width = (size_t)experts * ff;
+    const size_t routed = (size_t)experts * ff, width = routed + shared_ff;
     for (size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; gi < groups; gi += (size_t)gridDim.x * blockDim.x) {
         const size_t i = gi * N, r = i / width, col = i - r * width;
-        const float wt = weights[r * experts + col / ff];
+        const float wt = weights[r * ld_w + (col < routed ? col / ff : experts)];
         uint4 raw = *reinterpret_cast<const uint4*>(hidden + i);
         T* v = reinterpret_cast<T*>(&raw);
 #pragma unroll
@@ -206,13 +232,17 @@ JLLM_EXPORT int jllm_glu_clamped(const void* gate_up, const float* weights, void
     return jllm_check_launch("glu_clamped");
 }
 
-// h [rows, ld] of type `dtype` (the normed rows); router [experts, dim] float32; correction [experts] or null;
-// weights [rows, experts] float32.
+// h [rows, ld] of type `dtype` (the normed rows); router [experts + identity + gates, dim] float32; correction
+// [experts + identity] or null; weights [rows, ld_out] float32: the experts' weights, then the gates, then (with identity
+// entries) the sum of the chosen identity entries' weights.
 JLLM_EXPORT int jllm_route_experts(const void* h, int dtype, int ld, const float* router, const void* correction,
-                                   int correction_dtype, float* weights, int rows, int dim, int experts, int top, float scale,
-                                   int normalize, cudaStream_t stream) {
-    JLLM_REQUIRE(rows >= 0 && dim > 0 && experts > 0 && top >= 1 && top <= experts && experts <= 4096,
-                 "route_experts: rows=%d dim=%d experts=%d top=%d", rows, dim, experts, top);
+                                   int correction_dtype, float* weights, int rows, int dim, int real, int top, float scale,
+                                   int normalize, int identity, int gates, int softmax, int ld_out, cudaStream_t stream) {
+    const int experts = real + identity + gates;
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && real > 0 && identity >= 0 && gates >= 0 && top >= 1 && top <= real + identity &&
+                 experts <= 4096 && ld_out >= real + gates + (identity ? 1 : 0),
+                 "route_experts: rows=%d dim=%d experts=%d identity=%d gates=%d top=%d ld_out=%d", rows, dim, real, identity, gates,
+                 top, ld_out);
     if (rows == 0) return JLLM_OK;
     const VecRef c{correction, correction_dtype};
     const int padded = (experts + 1) / 2 * 2;       // the row's copy behind the two score arrays starts on 16 bytes
@@ -225,38 +255,40 @@ JLLM_EXPORT int jllm_route_experts(const void* h, int dtype, int ld, const float
     }
     if (dtype == JLLM_F32)
         jllm_launch(route_experts_kernel<float>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, (const float*)h, ld,
-                    router, c, (int)(correction != nullptr), weights, dim, experts, top, scale, normalize);
+                    router, c, (int)(correction != nullptr), weights, dim, real, top, scale, normalize, identity, gates, softmax, ld_out);
     else
         jllm_launch(route_experts_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT,
-                    (const __nv_bfloat16*)h, ld, router, c, (int)(correction != nullptr), weights, dim, experts, top, scale,
-                    normalize);
+                    (const __nv_bfloat16*)h, ld, router, c, (int)(correction != nullptr), weights, dim, real, top, scale,
+                    normalize, identity, gates, softmax, ld_out);
     return jllm_check_launch("route_experts");
 }
 
-// hidden [rows, experts * ff] (contiguous): the values of expert e are multiplied by weights[r, e].
+// hidden [rows, experts * ff + shared_ff] (contiguous): the values of expert e are multiplied by weights[r, e], the last
+// shared_ff values by weights[r, experts]; weights [rows, ld_w] float32.
 JLLM_EXPORT int jllm_scale_expert_hidden(void* hidden, int dtype, const float* weights, int rows, int experts, int ff,
-                                         cudaStream_t stream) {
-    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0, "scale_expert_hidden: rows=%d experts=%d ff=%d", rows, experts, ff);
+                                         int ld_w, int shared_ff, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0 && shared_ff >= 0 && ld_w >= experts + (shared_ff ? 1 : 0),
+                 "scale_expert_hidden: rows=%d experts=%d ff=%d shared_ff=%d ld_w=%d", rows, experts, ff, shared_ff, ld_w);
     if (rows == 0) return JLLM_OK;
-    const size_t total = (size_t)rows * experts * ff;
+    const size_t total = (size_t)rows * ((size_t)experts * ff + shared_ff);
     const int per = dtype == JLLM_F32 ? 4 : 8;
-    if (ff % per == 0 && ((uintptr_t)hidden % 16) == 0) {
+    if (ff % per == 0 && shared_ff % per == 0 && ((uintptr_t)hidden % 16) == 0) {
         const size_t groups = total / per;
         const int vblocks = (int)min((size_t)65535, (groups + 255) / 256);
         if (dtype == JLLM_F32)
             jllm_launch(scale_expert_hidden_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
-                        (float*)hidden, weights, experts, ff, groups);
+                        (float*)hidden, weights, experts, ff, groups, ld_w, shared_ff);
         else
             jllm_launch(scale_expert_hidden_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
-                        (__nv_bfloat16*)hidden, weights, experts, ff, groups);
+                        (__nv_bfloat16*)hidden, weights, experts, ff, groups, ld_w, shared_ff);
         return jllm_check_launch("scale_expert_hidden");
     }
     const int blocks = (int)min((size_t)65535, (total + 255) / 256);
     if (dtype == JLLM_F32)
         jllm_launch(scale_expert_hidden_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (float*)hidden,
-                    weights, experts, ff, total);
+                    weights, experts, ff, total, ld_w, shared_ff);
     else
         jllm_launch(scale_expert_hidden_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
-                    (__nv_bfloat16*)hidden, weights, experts, ff, total);
+                    (__nv_bfloat16*)hidden, weights, experts, ff, total, ld_w, shared_ff);
     return jllm_check_launch("scale_expert_hidden");
 }

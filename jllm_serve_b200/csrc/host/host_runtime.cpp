@@ -106,12 +106,15 @@ struct Cache {
     int page_size = 1, num_pages = 0;
     std::vector<int> windows;               // per paged group; 0 = every earlier position, w > 0 = the last w, -c < 0 = the
                                             // row's own chunk of c positions (position p lies in chunk p / c)
+    std::vector<int> kept;                  // per paged group: with a window, the request's first `kept` positions stay visible
+                                            // to every later row, so the pages that hold them are never given back
     std::vector<Pool> pools;
     Pool slots;
     std::unordered_map<long long, Request> requests;
     long long next_epoch = 1;
 
     int pages_for(int positions) const { return (positions + page_size - 1) / page_size; }
+    int kept_pages(int g) const { return windows[g] > 0 ? pages_for(kept[g]) : 0; }
     int first_needed_page(int g, int length) const {   // pages below hold only positions no later query can see
         const int w = windows[g];
         if (w == 0) return 0;
@@ -199,7 +202,7 @@ struct Cache {
             if ((long long)length > (long long)table.size() * page_size)
                 return fail(JH_BOOKKEEPING, "request #%lld committed %d positions beyond its pages", id, length);
             const int upto = std::min(first_needed_page((int)g, length), (int)table.size());
-            for (int i = 0; i < upto; ++i) {
+            for (int i = kept_pages((int)g); i < upto; ++i) {
                 if (table[i] == RELEASED) continue;
                 const int rc = pools[g].release(table[i], id);
                 if (rc != JH_OK) return rc;
@@ -299,12 +302,24 @@ JH_EXPORT void* jh_cache_new(int groups, const int* windows, int page_size, int 
     c->page_size = page_size;
     c->num_pages = num_pages;
     c->windows.assign(windows, windows + groups);
+    c->kept.assign(groups, 0);
     c->pools.resize(groups);
     for (int g = 0; g < groups; ++g) c->pools[g].init(num_pages, "group" + std::to_string(g) + " pages");
     c->slots.init(max_requests, "state slots");
     return c;
 }
 JH_EXPORT void jh_cache_delete(void* c) { delete static_cast<Cache*>(c); }
+
+// A windowed group whose requests keep their first `positions` positions visible: the pages of those are not given back.
+// To be said before any request is opened.
+JH_EXPORT int jh_cache_keep_first(void* cv, int group, int positions) {
+    Cache* c = static_cast<Cache*>(cv);
+    if (group < 0 || group >= (int)c->pools.size() || positions < 0)
+        return fail(JH_VALUE, "keep_first: group=%d of %d, positions=%d", group, (int)c->pools.size(), positions);
+    if (!c->requests.empty()) return fail(JH_VALUE, "keep_first: requests are open already");
+    c->kept[group] = positions;
+    return JH_OK;
+}
 
 JH_EXPORT int jh_cache_open(void* cv, long long id, int* slot_out) {
     Cache* c = static_cast<Cache*>(cv);

@@ -548,8 +548,10 @@ int launch_chunked(const void* proj, int ld, int v_off, const float* chunk_decay
     return jllm_check_launch("gla_chunk");
 }
 
-// y[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * gain * act(gate[r, h, :]) * scale, act = silu or (gate_kind 1)
-// sigmoid; one warp per (row, head). A norm over all heads together is the case heads = 1.
+// y[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * gain * act(gate[r, h, :]) * scale, act = silu or (gate_kind bit 0)
+// sigmoid; one warp per (row, head). A norm over all heads together is the case heads = 1. Bit 1 of gate_kind: the gate
+// comes first, y = rms(o * act(gate)) * gain * scale (the statistics are those of the gated values). Bit 2: the gain has a
+// value per column of the whole row (heads x dv) and not one per column of a head.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
@@ -560,16 +562,27 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
     if (w >= rows * heads) return;
     const int r = w / heads, h = w - r * heads;
     const float* src = o + ((size_t)r * heads + h) * dv;
+    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
+    const bool logistic = gate_kind & 1, gate_first = gate_kind & 2;
+    const int g0 = (gate_kind & 4) ? h * dv : 0;
+    auto gate_of = [&](int i) {
+        const float gv = to_float(gp[i]);
+        return (logistic ? 1.f : gv) / (1.f + expf(-gv));                          // silu, or (bit 0) the logistic function
+    };
     float ss = 0.f;
-    for (int i = lane; i < dv; i += 32) ss = fmaf(src[i], src[i], ss);
+    for (int i = lane; i < dv; i += 32) {
+        const float v = gate_first ? __fmul_rn(src[i], gate_of(i)) : src[i];
+        ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)dv + eps);
-    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
     T* dst = y + ((size_t)r * heads + h) * dv;
     for (int i = lane; i < dv; i += 32) {
-        const float gv = to_float(gp[i]);
-        const float gated = (gate_kind == 1 ? 1.f : gv) / (1.f + expf(-gv));       // silu, or (kind 1) the logistic function
-        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[i]), gated), scale));
+        const float gated = gate_of(i);
+        if (gate_first)
+            dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], gated), inv), gain[g0 + i]), scale));
+        else
+            dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[g0 + i]), gated), scale));
     }
 }
 
@@ -584,16 +597,27 @@ gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
     pdl_trigger();
     const int r = blockIdx.x / heads, h = blockIdx.x - r * heads;
     const float* src = o + ((size_t)r * heads + h) * dv;
+    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
+    const bool logistic = gate_kind & 1, gate_first = gate_kind & 2;
+    const int g0 = (gate_kind & 4) ? h * dv : 0;
+    auto gate_of = [&](int i) {
+        const float gv = to_float(gp[i]);
+        return (logistic ? 1.f : gv) / (1.f + expf(-gv));
+    };
     float ss = 0.f;
-    for (int i = threadIdx.x; i < dv; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+        const float v = gate_first ? __fmul_rn(src[i], gate_of(i)) : src[i];
+        ss = fmaf(v, v, ss);
+    }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)dv + eps);
-    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
     T* dst = y + ((size_t)r * heads + h) * dv;
     for (int i = threadIdx.x; i < dv; i += blockDim.x) {
-        const float gv = to_float(gp[i]);
-        const float gated = (gate_kind == 1 ? 1.f : gv) / (1.f + expf(-gv));
-        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[i]), gated), scale));
+        const float gated = gate_of(i);
+        if (gate_first)
+            dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], gated), inv), gain[g0 + i]), scale));
+        else
+            dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[g0 + i]), gated), scale));
     }
 }
 

@@ -142,7 +142,7 @@ class _Signatures:
     jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
-    jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
+    jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_decode_flat = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
@@ -176,8 +176,16 @@ class _Signatures:
     jllm_depth_mix = [P, ctypes.c_longlong, P, I, I, P, ctypes.c_longlong, P]
     jllm_scale_values = [P, F, ctypes.c_longlong, P]
     jllm_norm_add_mix = [P, P, P, I, I, I, F, I, P, ctypes.c_longlong, P, I, I, P, P, I, P, I, P, P, P, I, P]
-    jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
-    jllm_scale_expert_hidden = [P, I, P, I, I, I, P]
+    jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, I, I, I, I, P]
+    jllm_scale_expert_hidden = [P, I, P, I, I, I, I, I, P]
+    jllm_bounds_error_gated_recurrence = [P]
+    jllm_ssm_gates = [P, I, P, P, I, P, P, I, I, P]
+    jllm_memory_gates = [P, I, I, I, P, P, I, F, P, I, P, P, P, P, P, P, I, I, P]
+    jllm_causal_conv = [P, I, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P]
+    jllm_scalar_gated_recurrent = [P, I, I, I, P, I, I, I, P, I, I, I, P, P, P, P, I, P, P, I, P, P, P, P, I, I, I, I, F, P]
+    jllm_sigmoid_gate = [P, I, P, I, I, I, I, F, P]
+    jllm_activation = [P, I, ctypes.c_longlong, I, P]
+    jllm_add_rows_scaled = [P, P, I, I, P, I, I, I, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
 
@@ -276,14 +284,16 @@ def lightning_block_width(width: int = 0) -> None:
         raise KernelError(library().jllm_last_error().decode(errors="replace"))
 
 
-def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim, gate_kind: str = "silu") -> None:
+def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim, gate_kind: str = "silu", gate_first: bool = False,
+                    gain_per_column: bool = False) -> None:
     """out[r, h] = rmsnorm(o[r, h]) * gain * act(gate[r, h]) * scale over every head's value_dim values (act: "silu" or
     "sigmoid"); o float32 [rows, heads x value_dim], gate a view [rows, heads x value_dim] with any row stride, out contiguous
-    like gate's type. heads = 1 norms all of a row together."""
+    like gate's type. heads = 1 norms all of a row together. `gate_first`: rmsnorm(o * act(gate)) * gain * scale instead.
+    `gain_per_column`: the gain has heads x value_dim values, one per column of the row, and not value_dim for every head."""
     assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.dtype == out.dtype
     _call("jllm_gated_head_norm", o.data_ptr(), gate.data_ptr(), _DT[gate.dtype], gate.stride(0), gain.data_ptr(),
           _DT[gain.dtype], out.data_ptr(), o.shape[0], heads, value_dim, float(eps), float(scale),
-          {"silu": 0, "sigmoid": 1}[gate_kind], _stream())
+          {"silu": 0, "sigmoid": 1}[gate_kind] | (2 if gate_first else 0) | (4 if gain_per_column else 0), _stream())
 
 
 def latent_norm_store(src, gain, eps, slots, cache) -> None:
@@ -419,21 +429,105 @@ def scale_values(x, s: float) -> None:
     _call("jllm_scale_values", x.data_ptr(), float(s), x.numel(), _stream())
 
 
-def route_experts(h, router, correction, top, scale, normalize, weights) -> None:
+def route_experts(h, router, correction, top, scale, normalize, weights, identity: int = 0, gates: int = 0,
+                  softmax: bool = False) -> None:
     """weights[r, e] = the weight of expert e for row r (0 where it is not among the row's `top`): scores sigmoid(router
-    h) in float32, choice by score + correction, chosen scores over their sum (+ 1e-20) if `normalize`, times scale."""
+    h) in float32 (or, with `softmax`, the softmax of router h over all entries), choice by score + correction, chosen
+    scores over their sum (+ 1e-20) if `normalize`, times scale. The router's rows: the experts, then `identity` entries
+    that are chosen like experts but have no weights (the sum of a row's chosen identity weights leaves in the LAST column
+    of `weights`), then `gates` rows that are not routed: sigmoid(row . h) * scale leaves in the columns behind the experts'.
+    weights [rows, experts + gates + (1 if identity)]."""
     assert router.dtype == torch.float32 and router.is_contiguous() and weights.dtype == torch.float32
-    assert weights.is_contiguous() and h.stride(1) == 1 and weights.shape == (h.shape[0], router.shape[0])
+    real = router.shape[0] - identity - gates
+    assert weights.is_contiguous() and h.stride(1) == 1 and weights.shape == (h.shape[0], real + gates + (1 if identity else 0))
     _call("jllm_route_experts", h.data_ptr(), _DT[h.dtype], h.stride(0), router.data_ptr(), _p(correction),
           _DT[correction.dtype] if correction is not None else F32, weights.data_ptr(), h.shape[0], h.shape[1],
-          router.shape[0], int(top), float(scale), int(bool(normalize)), _stream())
+          real, int(top), float(scale), int(bool(normalize)), int(identity), int(gates), int(bool(softmax)), weights.shape[1],
+          _stream())
 
 
-def scale_expert_hidden(hidden, weights, ff) -> None:
-    """hidden[r, e * ff + j] *= weights[r, e], in place; hidden contiguous [rows, experts x ff]."""
+def scale_expert_hidden(hidden, weights, ff, experts: int = 0, shared_ff: int = 0) -> None:
+    """hidden[r, e * ff + j] *= weights[r, e], in place; hidden contiguous [rows, experts x ff + shared_ff], the last
+    shared_ff values times weights[r, experts]. `experts` 0: every column of `weights` is an expert's."""
     assert hidden.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
     _call("jllm_scale_expert_hidden", hidden.data_ptr(), _DT[hidden.dtype], weights.data_ptr(), hidden.shape[0],
-          weights.shape[1], int(ff), _stream())
+          int(experts or weights.shape[1]), int(ff), weights.shape[1], int(shared_ff), _stream())
+
+
+def ssm_gates(dt_raw, dt_bias, a_log, log_decay, in_scale) -> None:
+    """Per (row, head): dt = softplus(dt_raw + dt_bias); log_decay = -exp(a_log) dt; in_scale = dt. dt_raw a float32 view
+    [rows, heads]; the outputs float32 [rows, heads], contiguous."""
+    assert dt_raw.dtype == log_decay.dtype == in_scale.dtype == torch.float32 and dt_raw.stride(1) == 1
+    assert dt_bias.dtype == a_log.dtype and log_decay.is_contiguous() and in_scale.is_contiguous()
+    _call("jllm_ssm_gates", dt_raw.data_ptr(), dt_raw.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), _DT[a_log.dtype],
+          log_decay.data_ptr(), in_scale.data_ptr(), dt_raw.shape[0], dt_raw.shape[1], _stream())
+
+
+def memory_gates(raw, i_off, f_off, i_bias, f_bias, cap, m_state, batch, log_decay, in_scale, floor, heads) -> None:
+    """The exponential gates of a matrix memory, held in range by a running maximum m (a state [slots, heads] float32,
+    0 for a new request): i = cap tanh((raw_i + bi) / cap), f = logsigmoid(cap tanh((raw_f + bf) / cap)), m' = max(f + m, i),
+    log_decay = f + m - m', in_scale = exp(i - m'), floor = exp(-m'). raw a float32 view [rows, *]."""
+    assert raw.dtype == m_state.dtype == torch.float32 and raw.stride(1) == 1 and m_state.is_contiguous()
+    assert i_bias.dtype == f_bias.dtype and all(t.dtype == torch.float32 and t.is_contiguous() for t in (log_decay, in_scale, floor))
+    _call("jllm_memory_gates", raw.data_ptr(), raw.stride(0), int(i_off), int(f_off), i_bias.data_ptr(), f_bias.data_ptr(),
+          _DT[i_bias.dtype], float(cap), m_state.data_ptr(), m_state.shape[0], batch.seg_start.data_ptr(),
+          batch.seg_len.data_ptr(), batch.state_slots.data_ptr(), log_decay.data_ptr(), in_scale.data_ptr(), floor.data_ptr(),
+          batch.seg_start.numel(), int(heads), _stream())
+
+
+def causal_conv(u, off, channels, weight, bias, state, batch, out) -> None:
+    """out[t, c] = silu(bias[c] + sum_r weight[c, r] u[t - taps + 1 + r, off + c]) within a segment, the inputs in front of a
+    segment's first row taken from the request's state [slots, taps - 1, channels] (float32), which is then brought up to
+    date. u a view [rows, *]; out [rows, channels] of the compute type."""
+    taps = weight.shape[1]
+    assert weight.dtype == bias.dtype and weight.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous()
+    assert u.stride(1) == 1 and out.stride(1) == 1 and tuple(state.shape[1:]) == (taps - 1, channels)
+    global launch_count
+    launch_count += 0 if batch.decode_only or taps == 1 else 1
+    _call("jllm_causal_conv", u.data_ptr(), _DT[u.dtype], u.stride(0), int(off), weight.data_ptr(), bias.data_ptr(),
+          _DT[weight.dtype], state.data_ptr(), state.shape[0], batch.row_seg.data_ptr(), batch.seg_start.data_ptr(),
+          batch.seg_len.data_ptr(), batch.state_slots.data_ptr(), out.data_ptr(), _DT[out.dtype], out.stride(0), u.shape[0],
+          batch.seg_start.numel(), int(channels), int(taps), int(batch.decode_only), _stream())
+
+
+def scalar_gated_recurrent(q, q_off, q_groups, k, k_off, k_groups, v, v_off, log_decay, in_scale, state, batch, out, heads,
+                           key_dim, value_dim, query_scale: float = 1.0, skip=None, normalizer=None, floor=None) -> None:
+    """Per (request, head): S = exp(log_decay) S + (in_scale k) v^T, o = S^T (query_scale q) [+ skip_head v]; with a
+    `normalizer` state [slots, heads, key_dim] n = exp(log_decay) n + in_scale k and o / (max(|n . query_scale q|, floor) +
+    1e-6). q, k, v: views of one type whose heads lie at the given columns (head h reads query group h // (heads //
+    q_groups), key group likewise); log_decay, in_scale, floor float32 [rows, heads]; state [slots, heads, key_dim,
+    value_dim] float32, read and written in place; out float32 [rows, heads x value_dim]."""
+    assert q.dtype == k.dtype == v.dtype and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert state.dtype == out.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous()
+    assert log_decay.is_contiguous() and in_scale.is_contiguous() and (floor is None or floor.is_contiguous())
+    _call("jllm_scalar_gated_recurrent", q.data_ptr(), q.stride(0), int(q_off), int(q_groups), k.data_ptr(), k.stride(0),
+          int(k_off), int(k_groups), v.data_ptr(), v.stride(0), int(v_off), _DT[q.dtype], log_decay.data_ptr(),
+          in_scale.data_ptr(), _p(floor), _p(skip), _DT[skip.dtype] if skip is not None else F32, state.data_ptr(),
+          _p(normalizer), state.shape[0], batch.seg_start.data_ptr(), batch.seg_len.data_ptr(), batch.state_slots.data_ptr(),
+          out.data_ptr(), batch.seg_start.numel(), int(heads), int(key_dim), int(value_dim), float(query_scale), _stream())
+
+
+def sigmoid_gate(y, gate, scale: float = 1.0) -> None:
+    """y[r, i] *= sigmoid(gate[r, i]) * scale, in place; y and gate views [rows, width] of one type."""
+    assert y.dtype == gate.dtype and y.stride(1) == 1 and gate.stride(1) == 1 and y.shape == gate.shape
+    _call("jllm_sigmoid_gate", y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), _DT[y.dtype], y.shape[0], y.shape[1],
+          float(scale), _stream())
+
+
+ACTIVATIONS = {"gelu_erf": 1}
+
+
+def activation(x, kind: str) -> None:
+    """x = act(x) in place, x contiguous; kind "gelu_erf": z (1 + erf(z / sqrt 2)) / 2."""
+    assert x.is_contiguous()
+    _call("jllm_activation", x.data_ptr(), _DT[x.dtype], x.numel(), ACTIVATIONS[kind], _stream())
+
+
+def add_rows_scaled(x, h, weights) -> None:
+    """x[r, :] += weights[r] * h[r, :]; x float32 [rows, dim] contiguous, h a view [rows, dim], weights a float32 view [rows]."""
+    assert x.dtype == weights.dtype == torch.float32 and x.is_contiguous() and h.stride(1) == 1 and h.shape == x.shape
+    _call("jllm_add_rows_scaled", x.data_ptr(), h.data_ptr(), _DT[h.dtype], h.stride(0), weights.data_ptr(), weights.stride(0),
+          x.shape[0], x.shape[1], _stream())
 
 
 GLU_KINDS = {"silu": 1, "gelu_tanh": 2}      # the gate's activation as the kernels number it (GLU_* in common.cuh)
@@ -529,14 +623,15 @@ def norm_chain(x, a, gain_post, eps, b=None, gain_a=None, gain_b=None, scale: fl
 
 
 def attention_plain(q, q_stride, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads,
-                    head_dim, page_size, window, scale, value_dim: int = 0) -> None:
+                    head_dim, page_size, window, scale, value_dim: int = 0, keep_first: int = 0, sink=None) -> None:
     """`window`: 0 all earlier keys, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions.
+    `keep_first` (with a window): the request's first keys stay visible. `sink` [heads]: exp(sink) joins the denominator.
     `value_dim` (0: head_dim): the width of a value head where it differs from a key head's; the cache's rows are as
     wide as k_cache's last dimension says."""
     _call("jllm_attention_plain", q.data_ptr(), q_stride, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
           rows, heads, kv_heads, head_dim, int(value_dim or head_dim), k_cache.shape[-1], page_size, int(window),
-          float(scale), _DT[q.dtype], _stream())
+          float(scale), _DT[q.dtype], int(keep_first), _p(sink), _DT[sink.dtype] if sink is not None else F32, _stream())
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor, vocab: int | None = None) -> None:
@@ -777,7 +872,8 @@ def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swigl
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
-                "attention_prefill_pair", "rowwise", "linear_attention", "latent_attention", "residual_paths")
+                "attention_prefill_pair", "rowwise", "linear_attention", "latent_attention", "residual_paths",
+                "gated_recurrence")
 BOUNDS_WHAT = {1: "a block-table index", 2: "a page id", 3: "a cache slot", 4: "a token id", 5: "a row"}
 
 
@@ -999,12 +1095,12 @@ def _combine_launches(how, n, rows, kv_heads, head_dim) -> int:
 
 
 def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,
-              scratch=None, value_dim: int = 0) -> None:
+              scratch=None, value_dim: int = 0, keep_first: int = 0, sink=None) -> None:
     """Causal attention of every row of the batch over its own request's cached keys and values. `window`: 0 every
     earlier key, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions (position p lies in chunk
     p // c). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
     of one width only, so such a mixer runs on the plain kernel."""
-    one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim
+    one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim and not keep_first and sink is None
     if one_width and batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
         return _attention_decode_rows(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                       batch.rows, heads, kv_heads, head_dim, page_size, window, scale, batch.kv_bucket,
@@ -1026,7 +1122,12 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
                                    batch.kv_bucket, scratch)
         return
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
-                    batch.rows, heads, kv_heads, head_dim, page_size, window, scale, value_dim)
+                    batch.rows, heads, kv_heads, head_dim, page_size, window, scale, value_dim, keep_first, sink)
+
+
+def attention_tiles_take(keep_first: int, sink) -> bool:
+    """Whether the tile kernels (decode, prompt) take an attention with these extras; the plain kernel takes all."""
+    return not keep_first and sink is None
 
 
 def attention_prefill_fits(head_dim) -> bool:

@@ -51,6 +51,7 @@ class DecoderModel:
                                                                    names.final_norm, runtime)
         self.vocab, self.dim = core.vocab, core.dim
         self.logit_scale = float(getattr(core, "logit_scale", 1.0))
+        self.embedding_scale = float(getattr(core, "embedding_scale", 1.0))
         # depth mix: what run i hands on is a weighted sum of the embedded rows and of every run's result so far
         self.depth_weights = None
         if getattr(spec, "depth_mix", ""):
@@ -141,6 +142,8 @@ class DecoderModel:
         else:
             x = self.rt.buffer("residual", self.dim, torch.float32)[:rows]
         ops.embed_rows(batch.token_ids, self.embedding, x)
+        if self.embedding_scale != 1.0:
+            ops.scale_values(x, self.embedding_scale)
         for pe in self.position_encodings:
             pe.on_embedding(x, batch)
         for i, run in enumerate(schedule):

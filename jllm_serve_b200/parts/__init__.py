@@ -5,9 +5,11 @@ from .linear import Linear
 from .norm import DynamicTanh, LayerNorm, RmsNorm
 from .rope import RotaryTable
 from .attention import GqaAttention
-from .mlp import DenseGlu
+from .mlp import DenseGlu, DenseMlp
 from .linear_attention import FixedDecayLinearAttention, GatedLinearAttention
+from .state_space import SelectiveStateSpace
+from .matrix_memory import MatrixMemory
 from .parallel import ParallelMixers
 from .latent_attention import LatentAttention
 from .experts import RoutedExperts
-from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
+from .block import ParallelResidualBlock, PostNormBlock, PreNormBlock, SandwichNormBlock

@@ -14,6 +14,12 @@ the two); rotation of interleaved pairs; q and k divided by their root mean squa
 sees the earlier rows of its own chunk of the sequence only); a sigmoid gate per head, read from the mixer's input by rows
 that ride at the end of the stacked projection. These run through the general per-head kernel (`ops.head_prepare`) and
 the gate kernel; the attention itself is `ops.attention` for every form.
+
+Further: a window that keeps the sequence's first `keep_first` positions visible to every later row (they keep their true
+positions; the cache never gives their pages back); a learned sink per query head, a number whose exponential joins the
+softmax's denominator without a key or a value; a sigmoid gate of FULL width (one gate value per value of the concatenated
+heads, `gate = "sigmoid"`), whose rows also ride at the end of the stacked projection; and `out_scale`, a factor on the
+mixer's result that a mixer of mixers sets (applied together with the gate, in front of the output projection).
 """
 from __future__ import annotations
 
@@ -32,13 +38,15 @@ def _up8(n: int) -> int:
 
 class GqaAttention(Mixer):
     can_overwrite = True           # a block that norms the result before adding it asks for x = ... instead of x += ...
+    takes_out_scale = True         # `out_scale` multiplies the result (applied in front of the output product)
 
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, rope=None):
         self.spec, self.dim, self.rt, self.rope = spec, dim, runtime, rope
-        self.overwrite = False
+        self.overwrite, self.out_scale = False, 1.0
         H, Hkv, hd, vd, names = spec.heads, spec.kv_heads, spec.head_dim, spec.v_dim, spec.names
         self.q_width, self.k_width, self.v_width = H * hd, Hkv * hd, Hkv * vd
-        self.gated = spec.gate == "head_sigmoid"
+        self.gated = spec.gate in ("head_sigmoid", "sigmoid")
+        self.gate_width = H if spec.gate == "head_sigmoid" else H * vd      # gate values per row
         # the classic form (one head width, pairs (i, i + half), nothing behind the rotation) runs on the fused kernels that
         # were built for it; everything else on the general per-head kernel
         self.classic = (vd == hd and not spec.unit_qk and (rope is None or rope.pairing == "half"))
@@ -56,16 +64,18 @@ class GqaAttention(Mixer):
                 w.append(torch.zeros((pad, dim), dtype=g.dtype, device=g.device))
             w.append(g)
             # (and the row's width stays a multiple of 8 values: the tile kernels read queries by 16-byte pieces)
-            tail = _up8(H) - H
+            tail = _up8(self.gate_width) - self.gate_width
             if tail:
                 w.append(torch.zeros((tail, dim), dtype=g.dtype, device=g.device))
             if b:
-                b.append(torch.zeros((pad + H + tail,), dtype=b[0].dtype, device=b[0].device))
-            self.width = self.g_off + H + tail
+                b.append(torch.zeros((pad + self.gate_width + tail,), dtype=b[0].dtype, device=b[0].device))
+            self.width = self.g_off + self.gate_width + tail
         self.qkv = Linear(torch.cat(w, dim=0).contiguous(), torch.cat(b).contiguous() if b else None)
         self._q_only = None          # the query rows alone, made when a run first reads another run's cache
         del w, b
         self.out = Linear(tensors.pop(prefix + names.o), tensors.pop(prefix + names.o_bias) if spec.out_bias else None)
+        self.sink = tensors.pop(prefix + names.sink) if spec.sink else None
+        self.keep_first = int(getattr(spec, "keep_first", 0))
         self.q_gain = tensors.pop(prefix + names.q_norm) if spec.qk_norm else None
         self.k_gain = tensors.pop(prefix + names.k_norm) if spec.qk_norm else None
         if rope is not None and rope.rotary_dim > hd:
@@ -91,17 +101,23 @@ class GqaAttention(Mixer):
             out[prefix + names.k_norm] = TensorWant((hd,), "vector", init="gain")
         if spec.gate == "head_sigmoid":
             out[prefix + names.gate] = TensorWant((H, dim))
+        elif spec.gate == "sigmoid":
+            out[prefix + names.gate] = TensorWant((H * vd, dim))
+        if getattr(spec, "sink", False):
+            out[prefix + names.sink] = TensorWant((H,), "vector")
         return out
 
     @classmethod
     def cache_need(cls, spec):
         # a cache row holds a key in its first head_dim values and a value in its first value_dim; under a chunk mask the
         # pages of chunks that have passed are given back as under a window (the need's window is then -chunk)
-        return PagedKeysValues(spec.kv_heads, max(spec.head_dim, spec.v_dim), -spec.chunk if spec.chunk else spec.window)
+        return PagedKeysValues(spec.kv_heads, max(spec.head_dim, spec.v_dim), -spec.chunk if spec.chunk else spec.window,
+                               keep_first=int(getattr(spec, "keep_first", 0)))
 
     def _tiles_fit(self) -> bool:
         s = self.spec
-        return s.v_dim == s.head_dim and ops.attention_decode_fits(self.rt.dtype, s.heads, s.kv_heads, s.head_dim)
+        return (s.v_dim == s.head_dim and ops.attention_decode_fits(self.rt.dtype, s.heads, s.kv_heads, s.head_dim)
+                and ops.attention_tiles_take(self.keep_first, self.sink))
 
     def decode_bucket_cap(self, rows: int) -> int:
         s = self.spec
@@ -124,6 +140,7 @@ class GqaAttention(Mixer):
         att = self.rt.buffer("attention_out", s.heads * s.v_dim)[:rows]
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
         if (self.classic and not self.gated and cache.writes and batch.decode_only and rope is not None
+                and self.sink is None and not self.keep_first and self.out_scale == 1.0
                 and ops.attention_decode_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim)
                 and ops.attention_decode_fresh_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim, rope.rotary_dim)):
             # a step of single rows: the attention kernel norms and rotates its own rows and writes their keys and values
@@ -145,9 +162,15 @@ class GqaAttention(Mixer):
                              rope.pairing if rope else "half", s.unit_qk, batch.positions, slots, cache.keys, cache.values,
                              s.heads, s.kv_heads, s.head_dim, s.v_dim, self.rt.page_size, write_kv=cache.writes)
         ops.attention(qkv, cache.keys, cache.values, att, batch, cache.group, s.heads, s.kv_heads, s.head_dim,
-                      self.rt.page_size, self.span, s.scale, scratch, value_dim=s.v_dim)
-        if self.gated:
-            ops.head_gate(att, qkv[:, self.g_off:self.g_off + s.heads], s.heads, s.v_dim)
+                      self.rt.page_size, self.span, s.scale, scratch, value_dim=s.v_dim, keep_first=self.keep_first,
+                      sink=self.sink)
+        if s.gate == "sigmoid":
+            ops.sigmoid_gate(att, qkv[:, self.g_off:self.g_off + self.gate_width], self.out_scale)
+        else:
+            if self.gated:
+                ops.head_gate(att, qkv[:, self.g_off:self.g_off + s.heads], s.heads, s.v_dim)
+            if self.out_scale != 1.0:
+                raise ops.KernelError("a factor on the attention's result is built together with the gate of full width")
         self.out.forward(att, x, accumulate=not self.overwrite)
 
 

@@ -98,6 +98,36 @@ class PreNormBlock(Block):
 register_block("pre_norm", PreNormBlock, replace=True)
 
 
+class ParallelResidualBlock(PreNormBlock):
+    """ONE norm whose result feeds both parts, and both results are added to the stream:
+
+        h = norm(x);   x += mixer(h) + feed_forward(h)
+
+    Both parts add into the float32 stream themselves, one after the other (the add is the epilogue of their last products);
+    neither reads what the other wrote, because both read h. The layer's one gain is `names.mixer_norm`."""
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, position_encodings):
+        if spec.feed_forward is not None and spec.names.feed_forward_norm != spec.names.mixer_norm:
+            raise ValueError("one norm feeds both parts: the feed-forward's norm is named like the mixer's")
+        super().__init__(spec, dim, tensors, prefix, runtime, position_encodings)
+        self.ffn_norm = None           # (built by the base from the same tensor; there is one norm)
+
+    def forward(self, x, batch, cache) -> None:
+        xb = self.rt.buffer("normed", self.dim)[:x.shape[0]]
+        self.mixer_norm.forward(x, xb)
+        y = self._into(self.mixer, x)
+        self.mixer.forward(xb, y, batch, cache)
+        self._settle(x, y)
+        if self.feed_forward is None:
+            return
+        y = self._into(self.feed_forward, x)
+        self.feed_forward.forward(xb, y, batch)
+        self._settle(x, y)
+
+
+register_block("parallel_residual", ParallelResidualBlock, replace=True)
+
+
 class SandwichNormBlock(PreNormBlock):
     """A norm in front of each part and one behind it, before the residual sum:
 

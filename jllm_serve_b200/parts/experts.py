@@ -14,6 +14,13 @@ Both of an expert's first products are linear, so w_e (Wgate_e h) and w_e (Wup_e
 stacked product runs once on h itself, and one kernel (`ops.glu_clamped`) multiplies, cuts off and gates. An expert that a
 row does not use has weight 0 and adds exact zeros, as above. `shared`: a dense gated feed-forward of its own sizes that
 every row runs, added to the same result.
+
+What a spec may ask of the router (`ops.route_experts`): `score` "softmax" (the scores are a softmax over all of the router's
+entries); `identity` entries behind the experts, chosen like experts, that have no weights and give the row's input itself
+times their weight (`ops.add_rows_scaled` with the sum of a row's chosen identity weights); `shared_gate`, a [1, dim] matrix
+whose logistic value per row multiplies the shared expert's result: its row rides behind the router's (one float32 matrix,
+one launch), and the shared expert rides behind the routed ones in both products as an expert that every row uses with that
+weight.
 """
 from __future__ import annotations
 
@@ -48,7 +55,15 @@ class RoutedExperts(FeedForward):
             gates.append(tensors.pop(prefix + "shared." + shared.names[0]))
             ups.append(tensors.pop(prefix + "shared." + shared.names[1]))
             downs.append(tensors.pop(prefix + "shared." + shared.names[2]))
+        elif shared is not None and getattr(spec, "shared_gate", "") and shared.kind == "dense_glu" and shared.activation == spec.activation:
+            # a gated shared expert (weights on the output): behind the routed ones in both products, its weight the row's gate
+            self.shared_ff = shared.hidden
+            gates.append(tensors.pop(prefix + "shared." + shared.names[0]))
+            ups.append(tensors.pop(prefix + "shared." + shared.names[1]))
+            downs.append(tensors.pop(prefix + "shared." + shared.names[2]))
         elif shared is not None:
+            if getattr(spec, "shared_gate", ""):
+                raise ValueError("a gate on a shared expert of another kind of unit than the routed ones is not built")
             self.shared = part_class("feed_forward", shared.kind)(shared, dim, tensors, prefix + "shared.", runtime)
         self.hidden = E * ff + self.shared_ff
         gate, up = torch.cat(gates, dim=0), torch.cat(ups, dim=0)
@@ -66,12 +81,23 @@ class RoutedExperts(FeedForward):
         del downs
         self.router = tensors.pop(prefix + "router")
         self.correction = tensors.pop(prefix + "correction") if spec.correction else None
+        self.identity = int(getattr(spec, "identity", 0))
+        self.softmax = getattr(spec, "score", "sigmoid") == "softmax"
+        self.gates = 0
+        if getattr(spec, "shared_gate", ""):
+            self.gates = 1
+            self.router = torch.cat([self.router, tensors.pop(prefix + spec.shared_gate).to(self.router.dtype)], dim=0).contiguous()
+        # a row's table: the experts' weights, the shared expert's gate, the sum of its chosen identity entries' weights
+        self.table = E + self.gates + (1 if self.identity else 0)
 
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
-        out = {prefix + "router": TensorWant((spec.experts, dim), "matrix_fp32")}
+        entries = spec.experts + int(getattr(spec, "identity", 0))
+        out = {prefix + "router": TensorWant((entries, dim), "matrix_fp32")}
         if spec.correction:
-            out[prefix + "correction"] = TensorWant((spec.experts,), "vector")
+            out[prefix + "correction"] = TensorWant((entries,), "vector")
+        if getattr(spec, "shared_gate", ""):
+            out[prefix + spec.shared_gate] = TensorWant((1, dim), "matrix_fp32")
         for e in range(spec.experts):
             out[f"{prefix}e{e}.gate"] = TensorWant((spec.hidden, dim))
             out[f"{prefix}e{e}.up"] = TensorWant((spec.hidden, dim))
@@ -82,8 +108,9 @@ class RoutedExperts(FeedForward):
 
     def forward(self, xb, x, batch) -> None:
         s, rows = self.spec, xb.shape[0]
-        weights = self.rt.buffer("expert_weights", s.experts, torch.float32)[:rows]
-        ops.route_experts(xb, self.router, self.correction, s.top, s.scale * self.residual_scale, s.normalize, weights)
+        weights = self.rt.buffer("expert_weights", self.table, torch.float32)[:rows]
+        ops.route_experts(xb, self.router, self.correction, s.top, s.scale * self.residual_scale, s.normalize, weights,
+                          identity=self.identity, gates=self.gates, softmax=self.softmax)
         h = self.rt.buffer("experts_hidden", self.hidden)[:rows]
         if self.on_input:
             gate_up = self.rt.buffer("experts_gate_up", 2 * self.hidden)[:rows]
@@ -96,8 +123,10 @@ class RoutedExperts(FeedForward):
                 gate_up = self.rt.buffer("experts_gate_up", 2 * self.hidden)[:rows]
                 self.gate_up.forward(xb, gate_up)
                 ops.swiglu(gate_up, h)
-            ops.scale_expert_hidden(h, weights, s.hidden)
+            ops.scale_expert_hidden(h, weights, s.hidden, s.experts, self.shared_ff)
         self.down.forward(h, x, accumulate=not self.overwrite)
+        if self.identity:
+            ops.add_rows_scaled(x, xb, weights[:, self.table - 1])
         if self.shared is not None:
             self.shared.forward(xb, x, batch)          # (adds: its `overwrite` stays off)
 

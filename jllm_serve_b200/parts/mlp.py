@@ -63,3 +63,27 @@ class DenseGlu(FeedForward):
 
 
 register_feed_forward("dense_glu", DenseGlu, replace=True)
+
+
+class DenseMlp(FeedForward):
+    """x += Wdown act(Wup xb): two matrices and no gate; act the erf form of GELU, applied in place between the products."""
+    can_overwrite = True
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
+        self.hidden, self.dim, self.rt, self.activation = spec.hidden, dim, runtime, spec.activation
+        self.overwrite = False
+        self.up = Linear(tensors.pop(prefix + spec.names[0]))
+        self.down = Linear(tensors.pop(prefix + spec.names[1]))
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        return {prefix + spec.names[0]: TensorWant((spec.hidden, dim)), prefix + spec.names[1]: TensorWant((dim, spec.hidden))}
+
+    def forward(self, xb, x, batch) -> None:
+        h = self.rt.buffer("ffn_hidden", self.hidden)[:xb.shape[0]]
+        self.up.forward(xb, h)
+        ops.activation(h, self.activation)
+        self.down.forward(h, x, accumulate=not self.overwrite)
+
+
+register_feed_forward("dense_mlp", DenseMlp, replace=True)

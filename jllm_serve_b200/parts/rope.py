@@ -3,7 +3,8 @@
 cos[p, i] = (float) cos(p * f_i), f_i = theta^(-2i / rotary_dim), the angle formed in
 double precision and rounded once (src/main/java/org/robomiri/jllm/model/Rope.java:24-38,
 122-127); `linear` divides every frequency by the factor (:138-142); `yarn` blends plain and
-divided frequencies over a ramp and scales cos and sin by an amplitude (:75-85,170-208).
+divided frequencies over a ramp and scales cos and sin by an amplitude (:75-85,170-208);
+`banded` (not in the reference) keeps, divides or blends a frequency by its wavelength.
 The table is made once for the engine's context and lives on the device in float32; the
 rotation itself is fused into the mixer's kernel, which takes the table, `rotary_dim` and
 the pairing as parameters.
@@ -37,6 +38,20 @@ def inverse_frequencies(spec, max_positions: int) -> torch.Tensor:
             plain = 1.0 / math.pow(theta, (2.0 * i) / d)
             ramp = min(max((i - low) / span, 0), 1)
             f[i] = plain / sc.factor * ramp + plain * (1 - ramp)
+    elif sc.kind == "banded":
+        # by wavelength: short waves (below original / high) stay, long ones (above original / low) are divided by the factor,
+        # those in between blend the two in proportion to where original / wavelength lies between low and high
+        orig = float(sc.original_max_positions or max_positions)
+        for i in range(half):
+            plain = f[i]
+            length = 2 * math.pi / plain
+            if length < orig / sc.high:
+                continue
+            if length > orig / sc.low:
+                f[i] = plain / sc.factor
+            else:
+                s = (orig / length - sc.low) / (sc.high - sc.low)
+                f[i] = (1 - s) * plain / sc.factor + s * plain
     elif sc.kind != "none":
         raise ValueError(f"rope scaling {sc.kind!r} is not built")
     return torch.tensor(f, dtype=torch.float64)
