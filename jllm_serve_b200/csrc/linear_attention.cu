@@ -552,9 +552,9 @@ int launch_chunked(const void* proj, int ld, int v_off, const float* chunk_decay
 // sigmoid; one warp per (row, head). A norm over all heads together is the case heads = 1. Bit 1 of gate_kind: the gate
 // comes first, y = rms(o * act(gate)) * gain * scale (the statistics are those of the gated values). Bit 2: the gain has a
 // value per column of the whole row (heads x dv) and not one per column of a head.
-template <typename T>
+template <typename T, typename TG = T>
 __global__ void __launch_bounds__(256)
-gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
+gated_head_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
                        int rows, int heads, int dv, float eps, float scale, int gate_kind) {
     pdl_wait();
     pdl_trigger();
@@ -562,7 +562,7 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
     if (w >= rows * heads) return;
     const int r = w / heads, h = w - r * heads;
     const float* src = o + ((size_t)r * heads + h) * dv;
-    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
+    const TG* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
     const bool logistic = gate_kind & 1, gate_first = gate_kind & 2;
     const int g0 = (gate_kind & 4) ? h * dv : 0;
     auto gate_of = [&](int i) {
@@ -588,16 +588,16 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
 
 // The same with a block per (row, head), for norms over many values (all heads of a row together: thousands): a warp
 // alone would walk them one after the other.
-template <typename T>
+template <typename T, typename TG = T>
 __global__ void __launch_bounds__(256)
-gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
+gated_row_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
                       int heads, int dv, float eps, float scale, int gate_kind) {
     __shared__ float scratch[33];
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.x / heads, h = blockIdx.x - r * heads;
     const float* src = o + ((size_t)r * heads + h) * dv;
-    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
+    const TG* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
     const bool logistic = gate_kind & 1, gate_first = gate_kind & 2;
     const int g0 = (gate_kind & 4) ? h * dv : 0;
     auto gate_of = [&](int i) {
@@ -1052,15 +1052,23 @@ JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off,
 
 JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype, int ld_gate, const void* gain,
                                      int gain_dtype, void* y, int rows, int heads, int dv, float eps, float scale,
-                                     int gate_kind, cudaStream_t stream) {
+                                     int gate_kind, int gate_dtype, cudaStream_t stream) {
+    // `dtype`: the type of y; `gate_dtype`: the gate's (the same, or float32 beside a bfloat16 y: a gate that a product left
+    // in float32)
     JLLM_REQUIRE(rows >= 0 && heads > 0 && dv > 0, "gated_head_norm: rows=%d heads=%d dv=%d", rows, heads, dv);
+    JLLM_REQUIRE(gate_dtype == dtype || gate_dtype == JLLM_F32, "gated_head_norm: a gate of type %d beside a result of type %d",
+                 gate_dtype, dtype);
     if (rows == 0) return JLLM_OK;
     const VecRef g{gain, gain_dtype};
     const long long warps = (long long)rows * heads;
+    const bool wide_gate = gate_dtype != dtype;
     if (dv > 512 && warps <= 2147483647ll) {       // long norms: a block each
         if (dtype == JLLM_F32)
             jllm_launch(gated_row_norm_kernel<float>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
                         (const float*)gate, ld_gate, g, (float*)y, heads, dv, eps, scale, gate_kind);
+        else if (wide_gate)
+            jllm_launch(gated_row_norm_kernel<__nv_bfloat16, float>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
+                        (const float*)gate, ld_gate, g, (__nv_bfloat16*)y, heads, dv, eps, scale, gate_kind);
         else
             jllm_launch(gated_row_norm_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
                         (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, heads, dv, eps, scale, gate_kind);
@@ -1070,6 +1078,9 @@ JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype
     if (dtype == JLLM_F32)
         jllm_launch(gated_head_norm_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o, (const float*)gate,
                     ld_gate, g, (float*)y, rows, heads, dv, eps, scale, gate_kind);
+    else if (wide_gate)
+        jllm_launch(gated_head_norm_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
+                    (const float*)gate, ld_gate, g, (__nv_bfloat16*)y, rows, heads, dv, eps, scale, gate_kind);
     else
         jllm_launch(gated_head_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
                     (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, rows, heads, dv, eps, scale, gate_kind);

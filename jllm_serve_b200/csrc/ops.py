@@ -158,7 +158,7 @@ class _Signatures:
     jllm_add_scaled = [P, P, F, ctypes.c_longlong, P]
     jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P, I, P]
     jllm_gla_chunked = [P, I, I, I, I, I, P, I, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, F, P, I, P]
-    jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, I, P]
+    jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, I, I, P]
     jllm_lightning_block_width = [I]
     jllm_head_prepare = [P, I, I, I, I, I, P, P, I, I, I, F, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     jllm_head_gate = [P, I, I, P, I, I, I, I, P]
@@ -288,12 +288,12 @@ def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim, gate_kind:
                     gain_per_column: bool = False) -> None:
     """out[r, h] = rmsnorm(o[r, h]) * gain * act(gate[r, h]) * scale over every head's value_dim values (act: "silu" or
     "sigmoid"); o float32 [rows, heads x value_dim], gate a view [rows, heads x value_dim] with any row stride, out contiguous
-    like gate's type. heads = 1 norms all of a row together. `gate_first`: rmsnorm(o * act(gate)) * gain * scale instead.
+    of gate's type (or bfloat16 beside a float32 gate). heads = 1 norms all of a row together. `gate_first`: rmsnorm(o * act(gate)) * gain * scale instead.
     `gain_per_column`: the gain has heads x value_dim values, one per column of the row, and not value_dim for every head."""
-    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.dtype == out.dtype
-    _call("jllm_gated_head_norm", o.data_ptr(), gate.data_ptr(), _DT[gate.dtype], gate.stride(0), gain.data_ptr(),
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.dtype in (out.dtype, torch.float32)
+    _call("jllm_gated_head_norm", o.data_ptr(), gate.data_ptr(), _DT[out.dtype], gate.stride(0), gain.data_ptr(),
           _DT[gain.dtype], out.data_ptr(), o.shape[0], heads, value_dim, float(eps), float(scale),
-          {"silu": 0, "sigmoid": 1}[gate_kind] | (2 if gate_first else 0) | (4 if gain_per_column else 0), _stream())
+          {"silu": 0, "sigmoid": 1}[gate_kind] | (2 if gate_first else 0) | (4 if gain_per_column else 0), _DT[gate.dtype], _stream())
 
 
 def latent_norm_store(src, gain, eps, slots, cache) -> None:
@@ -481,7 +481,7 @@ def causal_conv(u, off, channels, weight, bias, state, batch, out) -> None:
     date. u a view [rows, *]; out [rows, channels] of the compute type."""
     taps = weight.shape[1]
     assert weight.dtype == bias.dtype and weight.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous()
-    assert u.stride(1) == 1 and out.stride(1) == 1 and tuple(state.shape[1:]) == (taps - 1, channels)
+    assert u.stride(1) == 1 and out.stride(1) == 1 and tuple(state.shape[1:]) == (max(taps - 1, 1), channels)
     global launch_count
     launch_count += 0 if batch.decode_only or taps == 1 else 1
     _call("jllm_causal_conv", u.data_ptr(), _DT[u.dtype], u.stride(0), int(off), weight.data_ptr(), bias.data_ptr(),

@@ -10,8 +10,7 @@ With h the normed rows, per head (dk key channels, dv value channels):
     x += Wo ( rms(o_t) per head * n * sigmoid(Wg h) )                                       n: a gain over all heads
 
 One stacked input product (q, k, v, the gate and the two log gates' rows) leaves in float32, so that the gates and all that
-enters the recurrence beside q, k and v are 32-bit numbers in both precisions; q, k and v are rounded to the compute type
-where the recurrence fetches them. A request keeps three states of fixed size, float32, zero when it opens: S [heads, dk,
+enters the recurrence are 32-bit numbers in both precisions (the recurrence reads q, k and v as the product left them). A request keeps three states of fixed size, float32, zero when it opens: S [heads, dk,
 dv], n [heads, dk], m [heads]. The recurrence is `ops.scalar_gated_recurrent` with its normalizer; the gate kernel
 (`ops.memory_gates`) walks a request's tokens in order, because the maximum is a chain.
 """
@@ -82,17 +81,13 @@ class MatrixMemory(Mixer):
         b = self.rt.buffer("recurrence_in_scale", H, torch.float32)[:rows]
         floor = self.rt.buffer("recurrence_floor", H, torch.float32)[:rows]
         ops.memory_gates(proj, i_off, f_off, self.i_bias, self.f_bias, s.gate_cap, cache.states[2], batch, la, b, floor, H)
-        if self.rt.dtype == torch.float32:
-            qkv, base = proj, 0
-        else:                          # q, k, v and the gate in the compute type, as a product would have left them
-            qkv = self.rt.buffer("memory_qkvg", i_off)[:rows]
-            qkv.copy_(proj[:, :i_off])
-            base = 0
         o = self.rt.buffer("memory_out", H * dv, torch.float32)[:rows]
-        ops.scalar_gated_recurrent(qkv, base + q_off, H, qkv, base + k_off, H, qkv, base + v_off, la, b, cache.states[0], batch, o,
-                                   H, dk, dv, dk ** -0.5, normalizer=cache.states[1], floor=floor)
+        # (q, k and v are read as the product left them, in float32: a head's divisor |n . q| may lie near 0, where every
+        # rounding of q or k in front of the recurrence would weigh most)
+        ops.scalar_gated_recurrent(proj, q_off, H, proj, k_off, H, proj, v_off, la, b, cache.states[0], batch, o, H, dk, dv,
+                                   dk ** -0.5, normalizer=cache.states[1], floor=floor)
         y = self.rt.buffer("memory_gated", H * dv)[:rows]
-        ops.gated_head_norm(o, qkv[:, g_off:g_off + H * dv], self.gain, s.norm_eps, self.out_scale, y, H, dv, "sigmoid",
+        ops.gated_head_norm(o, proj[:, g_off:g_off + H * dv], self.gain, s.norm_eps, self.out_scale, y, H, dv, "sigmoid",
                             gain_per_column=True)
         self.out.forward(y, x, accumulate=not self.overwrite)
 

@@ -10,7 +10,7 @@ With h the normed rows, inner = heads x head_dim, N = state, G = groups:
     x += Wo ( rms_parts(y * silu(z)) * n )                               the gate first, then the norm in `norm_groups` equal parts
 
 The input product leaves in float32, so that the step sizes, the decays and everything else that enters the recurrence
-beside the projections are 32-bit numbers in both precisions; the convolution writes x, B and C in the compute type. A
+beside the projections are 32-bit numbers in both precisions; the convolution reads and writes float32 too. A
 request keeps two states of fixed size: S [heads, N, head_dim] and the convolution's last taps - 1 inputs [taps - 1,
 channels], both float32, both zero when the request opens. The recurrence is `ops.scalar_gated_recurrent` (one decay per head
 and token; keys B and queries C shared by the heads of a group; the skip D), which other mixers share.
@@ -51,7 +51,7 @@ class SelectiveStateSpace(Mixer):
     @classmethod
     def cache_need(cls, spec):
         return (FixedState((spec.heads, spec.state, spec.head_dim), "float32"),
-                FixedState((spec.conv - 1, spec.conv_channels), "float32"))
+                FixedState((max(spec.conv - 1, 1), spec.conv_channels), "float32"))      # (a row even with one tap: no empty state)
 
     def decode_bucket_cap(self, rows: int) -> int:
         return 1                       # nothing here looks at the context's length
@@ -63,7 +63,7 @@ class SelectiveStateSpace(Mixer):
         H, P, N, G, inner, C = s.heads, s.head_dim, s.state, s.groups, s.inner, s.conv_channels
         proj = self.rt.buffer("ssm_proj", self.width, torch.float32)[:rows]
         self.inp.forward(xb, proj)
-        mixed = self.rt.buffer("ssm_conv", C)[:rows]
+        mixed = self.rt.buffer("ssm_conv", C, torch.float32)[:rows]
         ops.causal_conv(proj, inner, C, self.conv, self.conv_bias, cache.states[1], batch, mixed)
         la = self.rt.buffer("recurrence_log_decay", H, torch.float32)[:rows]
         b = self.rt.buffer("recurrence_in_scale", H, torch.float32)[:rows]
@@ -73,12 +73,8 @@ class SelectiveStateSpace(Mixer):
         ops.scalar_gated_recurrent(mixed, inner + G * N, G, mixed, inner, G, mixed, 0, la, b, cache.states[0], batch, y, H, N, P,
                                    1.0, skip=self.skip)
         gated = self.rt.buffer("ssm_gated", inner)[:rows]
-        zt = self.rt.buffer("ssm_z", inner)[:rows] if proj.dtype != gated.dtype else None
-        if zt is not None:
-            zt.copy_(proj[:, :inner])          # the gate's values in the compute type, as the other gated norms read them
-        z = zt if zt is not None else proj[:, :inner]
-        ops.gated_head_norm(y, z, self.gain, s.norm_eps, self.out_scale, gated, s.norm_groups, inner // s.norm_groups, "silu",
-                            gate_first=True, gain_per_column=True)
+        ops.gated_head_norm(y, proj[:, :inner], self.gain, s.norm_eps, self.out_scale, gated, s.norm_groups, inner // s.norm_groups,
+                            "silu", gate_first=True, gain_per_column=True)
         self.out.forward(gated, x, accumulate=not self.overwrite)
 
 

@@ -198,9 +198,11 @@ def state_space(h, w, p, mx, eps, state=None):
     return y @ w[p + "o"].T
 
 
-def matrix_memory(h, w, p, mx, eps, state=None):
+def matrix_memory(h, w, p, mx, eps, state=None, margins=None):
     """h [T, width] -> [T, width]: the right mixer of a `parallel_2` layer. `state` = {"S": [heads, dim, vdim], "n": [heads,
-    dim], "m": [heads]} is read and updated if given."""
+    dim], "m": [heads]} is read and updated if given. `margins` (a list) gets a tensor [T]: per row the smallest |n . q| over
+    the heads as a share of |n| |q| (where it is near 0 the head's result turns its sign on a rounding of q or k: the divisor
+    is |n . q| and the norm behind it keeps only the direction)."""
     H, dk, dv, cap = mx["heads"], mx["dim"], mx["vdim"], float(mx["gate_cap"])
     T = h.shape[0]
     q = (h @ w[p + "q"].T).view(T, H, dk) / math.sqrt(dk)
@@ -212,6 +214,7 @@ def matrix_memory(h, w, p, mx, eps, state=None):
                  "m": torch.zeros(H, dtype=h.dtype)}
     S, n, m = state["S"], state["n"], state["m"]
     o = torch.zeros(T, H, dv, dtype=h.dtype)
+    turn = torch.full((T,), float("inf"), dtype=h.dtype)
     for t in range(T):
         for hd in range(H):
             m_new = torch.maximum(fg[t, hd] + m[hd], ig[t, hd])
@@ -220,17 +223,20 @@ def matrix_memory(h, w, p, mx, eps, state=None):
             n[hd] = keep * n[hd] + take * k[t, hd]
             m[hd] = m_new
             o[t, hd] = (S[hd].T @ q[t, hd]) / (torch.maximum(torch.abs(n[hd] @ q[t, hd]), torch.exp(-m_new)) + 1e-6)
+            turn[t] = torch.minimum(turn[t], torch.abs(n[hd] @ q[t, hd]) / (n[hd].norm() * q[t, hd].norm() + 1e-300))
+    if margins is not None:
+        margins.append(turn)
     y = rms(o, eps).reshape(T, H * dv) * w[p + "norm"] * torch.sigmoid(h @ w[p + "g"].T)
     return y @ w[p + "o"].T
 
 
-def mixer(kind, h, w, p, mx, eps):
+def mixer(kind, h, w, p, mx, eps, turns=None):
     left = sink_attention(h, w, p + "left.", mx["left"])
     if kind == "parallel":
         right = state_space(h, w, p + "right.", mx["right"], eps)
         return 0.5 * (norm(left, w[p + "left.out"], eps) + norm(right, w[p + "right.out"], eps))
     if kind == "parallel_2":
-        right = matrix_memory(h, w, p + "right.", mx["right"], eps)
+        right = matrix_memory(h, w, p + "right.", mx["right"], eps, margins=turns)
         return float(mx["left_scale"]) * left + float(mx["right_scale"]) * right
     raise ValueError(kind)
 
@@ -247,12 +253,31 @@ def router_choice(h, w, p, r):
     return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20), s
 
 
-def feed_forward(h, w, p, f):
+def choice_margins(h, w, p, r):
+    """Per row: how far the last chosen entry's choice score lies above the first one left out, as a share of the sum of the
+    chosen scores (inf if all entries are chosen): a margin near 0 between two entries that both weigh next to nothing is no
+    close call."""
+    s = torch.softmax(h @ w[p + "router"].T, dim=-1)
+    c = s + w[p + "correction"]
+    top = int(r["top"])
+    if top >= s.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    order = torch.argsort(c, dim=-1, descending=True)
+    ranked = torch.gather(c, 1, order)
+    taken = torch.gather(s, 1, order[:, :top])
+    at_stake = torch.maximum(taken[:, -1], torch.gather(s, 1, order[:, top:top + 1])[:, 0]) / taken.sum(dim=-1)
+    margin = (ranked[:, top - 1] - ranked[:, top]) / taken.sum(dim=-1)
+    return torch.where(at_stake < 0.02, torch.full_like(margin, float("inf")), margin)
+
+
+def feed_forward(h, w, p, f, margins=None):
     if f["kind"] == "dense":
         return gelu_erf(h @ w[p + "up"].T) @ w[p + "down"].T
     r = f["router"]
     E = int(r["experts"])
     chosen, weights, _ = router_choice(h, w, p, r)
+    if margins is not None:
+        margins.append(choice_margins(h, w, p, r))
     y = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, we in zip(chosen[t].tolist(), weights[t]):
@@ -264,16 +289,18 @@ def feed_forward(h, w, p, f):
 
 # ---- the model ------------------------------------------------------------------------------------------------------
 
-def forward(cfg, w, tokens, layers_out=None):
-    """Logits [T, vocab] of one whole sequence; `layers_out` (a list) gets the residual stream after every layer."""
+def forward(cfg, w, tokens, layers_out=None, margins_out=None, turns_out=None):
+    """Logits [T, vocab] of one whole sequence; `layers_out` (a list) gets the residual stream after every layer,
+    `margins_out` (a list) one tensor [T] per routed feed-forward: the margin of every row's choice of experts; `turns_out`
+    (a list) one tensor [T] per matrix memory: how near a head's divisor is to turning its sign (see `matrix_memory`)."""
     x = w["embed"][torch.tensor(tokens)] * float(cfg.get("embedding", {}).get("scale", 1.0))
     eps = float(cfg["norm"]["eps"])
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = norm(x, w[p + "norm1"], eps)
-        y = mixer(layer["type"], h, w, p + "mix.", layer["mixer"], eps)
+        y = mixer(layer["type"], h, w, p + "mix.", layer["mixer"], eps, turns_out)
         if layer.get("mlp") is not None:
-            y = y + feed_forward(h, w, p + "mlp.", layer["mlp"])
+            y = y + feed_forward(h, w, p + "mlp.", layer["mlp"], margins_out)
         x = x + y
         if layers_out is not None:
             layers_out.append(x.clone())
