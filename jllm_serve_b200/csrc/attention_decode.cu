@@ -50,7 +50,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                         const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int head_dim,
                         int page_size, int num_pages, int window, float scale_log2, int splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int keep_first, VecRef sink, int has_sink) {
+    // `keep_first`: with a window, the request's first keys that stay visible; a row's visible keys are walked by an index
+    // that counts them in ascending order (see jllm_kept_keys). `sink`: a number per query head whose exponential joins the
+    // denominator (here where one block holds all of a row's keys, else in the combine kernel).
     extern __shared__ float smem[];  // [WARPS][16][head_dim] outputs, then [WARPS][16][2] (max, sum)
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -59,7 +62,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     pdl_trigger();
     const int P = row_pos[r];
     const int first = jllm_first_key(P, window);
-    const int n_keys = P + 1 - first;
+    const int kept = jllm_kept_keys(first, window, keep_first);
+    const int n_keys = kept + P + 1 - first;
+    auto key_at = [&](int u) { return u < kept ? u : first + (u - kept); };
     // the block's share of the keys, in whole 16-key blocks
     const int blocks_total = (n_keys + 15) >> 4;
     const int blocks_per_split = (blocks_total + splits - 1) / splits;
@@ -90,12 +95,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 
     const size_t page_stride = (size_t)kv_heads * page_size * head_dim;
     for (int blk = blk_lo + warp; blk < blk_hi; blk += WARPS) {
-        const int base = first + blk * 16;
+        const int base = blk * 16;            // (an index among the row's visible keys)
         // ---- scores of 16 keys: two 8-key tiles ----
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
-            const int key = base + tile * 8 + g;
+            const int key = key_at(base + tile * 8 + g);
             bool ok = key <= P;
             const __nv_bfloat16* krow = nullptr;
             if (ok) {
@@ -117,7 +122,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int key = base + tile * 8 + 2 * t + (i & 1);
+                const int key = key_at(base + tile * 8 + 2 * t + (i & 1));
                 s[tile][i] = key <= P ? s[tile][i] * scale_log2 : -INFINITY;
                 mx[i >> 1] = fmaxf(mx[i >> 1], s[tile][i]);
             }
@@ -146,7 +151,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         bool vok[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int key = base + 2 * t + (i & 1) + 8 * (i >> 1);
+            const int key = key_at(base + 2 * t + (i & 1) + 8 * (i >> 1));
             vok[i] = key <= P;
             vrow[i] = nullptr;
             if (vok[i]) {
@@ -229,6 +234,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             ll += mw == -INFINITY ? 0.f : sml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
         }
         if (splits == 1) {
+            if (has_sink) {            // (2^(sink - max) may overflow where every score lies far below the sink: the result is then 0)
+                const float sl = sink[head] * LOG2E;
+                const float top = fmaxf(mm, sl);
+                acc *= exp2f(mm - top);
+                ll = ll * exp2f(mm - top) + exp2f(sl - top);
+            }
             out[(size_t)r * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(acc / ll);
         } else {
             const size_t slot = ((size_t)r * heads + head) * splits + split;
@@ -246,7 +257,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 // out[r, head] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the splits, in the order of the splits
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int out_stride, int heads, int head_dim,
-                                         int splits) {
+                                         int splits, VecRef sink, int has_sink) {
     constexpr int MAX_SPLITS = 32;
     __shared__ float weight[MAX_SPLITS];
     __shared__ float inv_total;
@@ -262,9 +273,11 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
         float M = ms;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float sl = has_sink ? sink[head] * LOG2E : -INFINITY;      // the sink joins the maximum and the sum once
+        M = fmaxf(M, sl);
         const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
         weight[s] = w;
-        float L = 0.f;
+        float L = has_sink ? exp2f(sl - M) : 0.f;
         for (int i = 0; i < splits; ++i) L += __shfl_sync(0xffffffffu, ls * w, i);
         if (s == 0) inv_total = 1.f / L;
     }
@@ -300,7 +313,13 @@ namespace {
 int decode_split(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
                  const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
                  int kv_heads, int head_dim, int page_size, int window, float scale, int splits, float* scratch,
-                 const staged::Fresh& fresh, cudaStream_t stream) {
+                 const staged::Fresh& fresh, cudaStream_t stream, int keep_first = 0, const void* sink = nullptr,
+                 int sink_dtype = JLLM_F32) {
+    // (kept first keys and a sink are the general kernel's: the staged kernels stream whole runs of neighbouring keys)
+    const bool extras = keep_first > 0 || sink != nullptr;
+    const VecRef sk{sink, sink_dtype};
+    const int has_sink = sink != nullptr;
+    JLLM_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_decode: keep_first=%d needs a window", keep_first);
     JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_size > 0,
                  "attention_decode: rows=%d heads=%d kv_heads=%d page_size=%d", rows, heads, kv_heads, page_size);
     JLLM_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
@@ -318,7 +337,7 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
     float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
     const float scale_log2 = scale * LOG2E;
     const int hdc = (head_dim + 63) / 64;
-    if (head_dim == 64 || head_dim == 128 || head_dim == 256) {
+    if (!extras && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
         // the common head sizes stream the cache through a shared-memory ring (attention_decode_staged.cuh)
         // The last block of a (row, kv head) pair adds the pair's partials up itself where the library's counters reach,
         // up to 8 splits: with more (few rows, long ranges) one block's adding of all of a pair's parts is slower than
@@ -333,7 +352,7 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
         int rc2 = jllm_check_launch("attention_decode_staged");
         if (rc2 != JLLM_OK || splits == 1 || counters != nullptr) return rc2;
         jllm_launch(attention_combine_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
-                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits);
+                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits, VecRef{nullptr, JLLM_F32}, 0);
         return jllm_check_launch("attention_combine");
     }
     JLLM_REQUIRE(fresh.qkv == nullptr, "attention_decode: head_dim=%d has no kernel that norms and rotates its own row", head_dim);
@@ -345,18 +364,30 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
                                                  (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride,    \
                                                  row_seg, row_pos, block_tables, table_stride, heads, kv_heads,     \
                                                  head_dim, page_size, jllm_pool_pages(), window, scale_log2, splits, \
-                                                 part_o, part_ml);                                                  \
+                                                 part_o, part_ml, keep_first, sk, has_sink);                        \
     }
     if (hdc == 1) JLLM_LAUNCH(1) else if (hdc == 2) JLLM_LAUNCH(2) else if (hdc == 3) JLLM_LAUNCH(3) else JLLM_LAUNCH(4)
 #undef JLLM_LAUNCH
     int rc = jllm_check_launch("attention_decode");
     if (rc != JLLM_OK || splits == 1) return rc;
     attention_combine_kernel<<<dim3(rows, heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
-                                                                   heads, head_dim, splits);
+                                                                   heads, head_dim, splits, sk, has_sink);
     return jllm_check_launch("attention_combine");
 }
 
 }  // namespace
+
+// The same with a window that keeps the request's first `keep_first` keys visible and / or a sink per query head (`sink`
+// [heads] of type `sink_dtype`, or null): every head size on the general kernel.
+JLLM_EXPORT int jllm_attention_decode_extras(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                             int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
+                                             int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
+                                             int window, float scale, int splits, float* scratch, int keep_first,
+                                             const void* sink, int sink_dtype, cudaStream_t stream) {
+    return decode_split(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, rows,
+                        heads, kv_heads, head_dim, page_size, window, scale, splits, scratch, staged::Fresh{}, stream,
+                        keep_first, sink, sink_dtype);
+}
 
 JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                       int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,

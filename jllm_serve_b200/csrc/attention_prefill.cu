@@ -62,7 +62,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const int* __restrict__ seg_start, const int* __restrict__ seg_len,
                          const int* __restrict__ seg_kv_len, const int* __restrict__ block_tables, int table_stride,
                          int num_segs, int heads, int kv_heads, int page_size, int num_pages, int window,
-                         float scale_log2) {
+                         float scale_log2, int keep_first, VecRef sink, int has_sink) {
+    // `keep_first`: with a window, the request's first keys that stay visible to every row: the key tiles that hold them are
+    // walked in front of the window's tiles. `sink`: a number per query head whose exponential joins the denominator.
     constexpr int CHUNKS = HD / 8;               // 16-byte chunks per row
     constexpr int TILE_BYTES = BKV * HD * 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -97,6 +99,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
 
     const int first_key = jllm_first_key(pos0, window);     // (the tile's first row sees the earliest key)
     const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV;  // inclusive range of key tiles
+    // the tiles of the kept keys that lie in front of that range (the tile's last row has the latest first key, so it keeps most)
+    const int keep = window > 0 ? keep_first : 0;
+    const int kept_tiles = keep > 0 ? min(kt_lo, (jllm_kept_keys(jllm_first_key(pos_last, window), window, keep) + BKV - 1) / BKV) : 0;
+    const int n_steps = kept_tiles + kt_hi - kt_lo + 1;
+    auto tile_of = [&](int step) { return step < kept_tiles ? step : kt_lo + (step - kept_tiles); };
     const size_t page_stride = (size_t)kv_heads * page_size * HD;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
@@ -105,7 +112,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         for (int i = threadIdx.x; i < BKV * CHUNKS; i += THREADS) {
             const int r = i / CHUNKS, c = i % CHUNKS;
             const int key = kt * BKV + r;
-            bool ok = key >= first_key && key <= pos_last;
+            bool ok = (key >= first_key || key < keep) && key <= pos_last;
             size_t off = 0;
             if (ok) {
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
@@ -119,7 +126,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         }
         cp_async_commit();
     };
-    load_kv(kt_lo, 0);
+    load_kv(tile_of(0), 0);
 
     // ---- Q fragments of this warp's 16 rows ----
     cp_async_wait<1>();
@@ -143,10 +150,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         first_r[h] = jllm_first_key(pos_r[h], window);
     }
 
-    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
-        const int buf = (kt - kt_lo) & 1;
-        if (kt < kt_hi) {
-            load_kv(kt + 1, buf ^ 1);
+    for (int step = 0; step < n_steps; ++step) {
+        const int kt = tile_of(step), buf = step & 1;
+        if (step + 1 < n_steps) {
+            load_kv(tile_of(step + 1), buf ^ 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -178,7 +185,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             // a tile that every row of this warp sees whole (all keys at or before the warp's first position and
             // inside every row's window) needs no mask: true for all but the tiles on the diagonal and the window's edge
             const int warp_first = pos0 + min(warp * 16, rows_here - 1), warp_last = pos0 + min(warp * 16 + 15, rows_here - 1);
-            const bool whole = key0 + BKV - 1 <= warp_first && key0 >= jllm_first_key(warp_last, window);
+            const bool whole = key0 + BKV - 1 <= warp_first && (key0 >= jllm_first_key(warp_last, window) || key0 + BKV - 1 < keep);
             if (whole) {
     #pragma unroll
                 for (int j = 0; j < BKV / 8; ++j)
@@ -193,7 +200,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int key = key0 + j * 8 + 2 * t + (i & 1), P = pos_r[i >> 1];
-                        const bool vis = key <= P && key >= first_r[i >> 1];
+                        const bool vis = jllm_key_visible(key, P, first_r[i >> 1], keep);
                         s[j][i] = vis ? s[j][i] * scale_log2 : -INFINITY;
                         mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
                     }
@@ -250,6 +257,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     for (int h = 0; h < 2; ++h) {
         const int r = warp * 16 + g + 8 * h;
         if (r >= rows_here) continue;
+        if (has_sink) {                    // (2^(sink - max) may overflow where every score lies far below the sink: the result is 0)
+            const float sl = sink[head] * LOG2E;
+            l_run[h] += exp2f(sl - m_run[h]);
+        }
         const float inv = 1.f / l_run[h];
         __nv_bfloat16* dst = out + (size_t)(row0 + r) * out_stride + (size_t)head * HD;
 #pragma unroll
@@ -264,7 +275,7 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
            const int* seg_start, const int* seg_len, const int* seg_kv_len, const int* block_tables, int table_stride,
            int num_segs, int rows, int heads, int kv_heads, int page_size, int window, float scale,
-           cudaStream_t stream) {
+           cudaStream_t stream, int keep_first = 0, VecRef sink = VecRef{nullptr, JLLM_F32}) {
     const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKV * HD * 2;
     auto kern = attention_prefill_kernel<HD>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -272,7 +283,8 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                                           (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, seg_start,
                                           seg_len, seg_kv_len, block_tables, table_stride, num_segs, heads, kv_heads,
-                                          page_size, jllm_pool_pages(), window, scale * LOG2E);
+                                          page_size, jllm_pool_pages(), window, scale * LOG2E, keep_first, sink,
+                                          (int)(sink.p != nullptr));
     return jllm_check_launch("attention_prefill");
 }
 
@@ -282,11 +294,12 @@ JLLM_BOUNDS_READER(attention_prefill)
 
 JLLM_EXPORT int jllm_attention_prefill_fits(int head_dim) { return head_dim == 64 || head_dim == 128 || head_dim == 256; }
 
-JLLM_EXPORT int jllm_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+static int prefill_any(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                        int out_stride, const int* seg_start, const int* seg_len, const int* seg_kv_len,
                                        const int* block_tables, int table_stride, int num_segs, int rows, int heads,
                                        int kv_heads, int head_dim, int page_size, int window, float scale,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, int keep_first, VecRef sink) {
+    JLLM_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_prefill: keep_first=%d needs a window", keep_first);
     JLLM_REQUIRE(rows >= 0 && num_segs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_size > 0,
                  "attention_prefill: rows=%d segments=%d heads=%d kv_heads=%d page_size=%d", rows, num_segs, heads,
                  kv_heads, page_size);
@@ -297,9 +310,29 @@ JLLM_EXPORT int jllm_attention_prefill(const void* q, int q_stride, const void* 
     JLLM_REQUIRE(heads <= 65535, "attention_prefill: heads=%d", heads);
     if (rows == 0 || num_segs == 0) return JLLM_OK;
 #define JLLM_ARGS q, q_stride, k_cache, v_cache, out, out_stride, seg_start, seg_len, seg_kv_len, block_tables, \
-                  table_stride, num_segs, rows, heads, kv_heads, page_size, window, scale, stream
+                  table_stride, num_segs, rows, heads, kv_heads, page_size, window, scale, stream, keep_first, sink
     if (head_dim == 64) return launch<64>(JLLM_ARGS);
     if (head_dim == 128) return launch<128>(JLLM_ARGS);
     return launch<256>(JLLM_ARGS);
 #undef JLLM_ARGS
+}
+
+JLLM_EXPORT int jllm_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                       int out_stride, const int* seg_start, const int* seg_len, const int* seg_kv_len,
+                                       const int* block_tables, int table_stride, int num_segs, int rows, int heads,
+                                       int kv_heads, int head_dim, int page_size, int window, float scale,
+                                       cudaStream_t stream) {
+    return prefill_any(q, q_stride, k_cache, v_cache, out, out_stride, seg_start, seg_len, seg_kv_len, block_tables, table_stride,
+                       num_segs, rows, heads, kv_heads, head_dim, page_size, window, scale, stream, 0, VecRef{nullptr, JLLM_F32});
+}
+
+// The same with a window that keeps the request's first `keep_first` keys visible and / or a sink per query head.
+JLLM_EXPORT int jllm_attention_prefill_extras(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                              int out_stride, const int* seg_start, const int* seg_len, const int* seg_kv_len,
+                                              const int* block_tables, int table_stride, int num_segs, int rows, int heads,
+                                              int kv_heads, int head_dim, int page_size, int window, float scale,
+                                              int keep_first, const void* sink, int sink_dtype, cudaStream_t stream) {
+    return prefill_any(q, q_stride, k_cache, v_cache, out, out_stride, seg_start, seg_len, seg_kv_len, block_tables, table_stride,
+                       num_segs, rows, heads, kv_heads, head_dim, page_size, window, scale, stream, keep_first,
+                       VecRef{sink, sink_dtype});
 }

@@ -40,7 +40,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seg_start, const int* __restrict__ seg_len,
                             const int* __restrict__ seg_kv_len, const int* __restrict__ block_tables, int table_stride,
                             int num_segs, int heads, int kv_heads, int page_size, int page_shift, int num_pages, int window,
-                            float scale_log2, int* __restrict__ error_word) {
+                            float scale_log2, int* __restrict__ error_word, int keep_first, VecRef sink, int has_sink) {
+    // `keep_first`: with a window, the request's first keys that stay visible to every row: the key tiles that hold them are
+    // walked in front of the window's tiles (tile j of the walk is key tile tile_of(j)). `sink`: a number per query head
+    // whose exponential joins the row's sum at the end.
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -69,7 +72,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int row0 = seg_start[seg] + q0;
     const int pos0 = seg_kv_len[seg] - n_rows + q0, pos_last = pos0 + rows_here - 1;
     const int first_key = jllm_first_key(pos0, window);     // (the tile's first row sees the earliest key)
-    const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV, n_tiles = kt_hi - kt_lo + 1;
+    const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV;
+    const int keep = window > 0 ? keep_first : 0;
+    const int kept_tiles = keep > 0 ? min(kt_lo, (jllm_kept_keys(jllm_first_key(pos_last, window), window, keep) + BKV - 1) / BKV) : 0;
+    const int n_tiles = kept_tiles + kt_hi - kt_lo + 1;
+    auto tile_of = [&](int j) { return j < kept_tiles ? j : kt_lo + (j - kept_tiles); };
     const int* table = block_tables + (size_t)seg * table_stride;
 
     if (threadIdx.x == 0) {
@@ -109,8 +116,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_load_2d(s_q + HALF_BYTES, &map_q, head * HD + 64, row0, bar(Q_FULL));
         }
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int b = j & 1, key0 = (kt_lo + j) * BKV;
-            const bool whole = key0 >= first_key && key0 + BKV - 1 <= pos_last;   // every row is a live, written key
+            const int b = j & 1, key0 = tile_of(j) * BKV;
+            const bool whole = (key0 >= first_key || key0 + BKV - 1 < keep) && key0 + BKV - 1 <= pos_last;   // every row is a live, written key
             for (int which = 0; which < 2 && ok; ++which) {                        // 0: keys, 1: values
                 const int full = (which ? V_FULL : K_FULL) + b, empty = (which ? V_EMPTY : K_EMPTY) + b;
                 const uint32_t dst = which ? s_v(b) : s_k(b);
@@ -139,7 +146,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int i = lane; i < BKV * 16; i += 32) {
                         const int r = i >> 4, c = i & 15;
                         const int key = key0 + r;
-                        bool live = key >= first_key && key <= pos_last;
+                        bool live = (key >= first_key || key < keep) && key <= pos_last;
                         size_t off = 0;
                         if (live) {
                             const long long pg = jllm_page_of(table, key >> page_shift, table_stride, num_pages);
@@ -208,10 +215,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int b = j & 1, key0 = (kt_lo + j) * BKV;
+            const int b = j & 1, key0 = tile_of(j) * BKV;
             if (!mbar_wait(bar(S_FULL + b), (j >> 1) & 1u, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
-            const bool masked = key0 + BKV - 1 > pos0 || key0 < lo || key0 < jllm_first_key(pos_last, window);
+            const bool masked = key0 + BKV - 1 > pos0 ||
+                                ((key0 < lo || key0 < jllm_first_key(pos_last, window)) && key0 + BKV - 1 >= keep);
             // the row of S: four loads in flight, one wait
             uint32_t v[4][32];
 #pragma unroll
@@ -223,7 +231,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = key0 + c * 32 + i;
-                        if (!(key <= P && key >= lo)) v[c][i] = __float_as_uint(-INFINITY);
+                        if (!jllm_key_visible(key, P, lo, keep)) v[c][i] = __float_as_uint(-INFINITY);
                     }
             }
             // (four chains, then their maximum: one chain of 128 dependent comparisons is pure latency)
@@ -286,6 +294,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && !mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1u, abort_flag)) ok = false;
         if (ok) {
             tcgen05_fence_after();
+            if (has_sink) l += exp2f(sink[head] * LOG2E - m);      // (m: the reference point of every term of l)
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + (size_t)(row0 + r) * out_stride + (size_t)head * HD;
 #pragma unroll 1
@@ -353,11 +362,13 @@ JLLM_EXPORT int jllm_attention_prefill_tc_error() {
     return v;
 }
 
-JLLM_EXPORT int jllm_attention_prefill_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+static int prefill_tc_any(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                           long long cache_pages, void* out, int out_stride, const int* seg_start,
                                           const int* seg_len, const int* seg_kv_len, const int* block_tables,
                                           int table_stride, int num_segs, int rows, int heads, int kv_heads,
-                                          int head_dim, int page_size, int window, float scale, cudaStream_t stream) {
+                                          int head_dim, int page_size, int window, float scale, cudaStream_t stream,
+                                          int keep_first, VecRef sink) {
+    JLLM_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_prefill_tc: keep_first=%d needs a window", keep_first);
     JLLM_REQUIRE(rows >= 0 && num_segs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && cache_pages > 0,
                  "attention_prefill_tc: rows=%d segments=%d heads=%d kv_heads=%d pages=%lld", rows, num_segs, heads,
                  kv_heads, cache_pages);
@@ -386,6 +397,28 @@ JLLM_EXPORT int jllm_attention_prefill_tc(const void* q, int q_stride, const voi
     jllm_launch(kern, grid, dim3(THREADS), SMEM_BYTES, stream, true, map_q, map_k, map_v, (const __nv_bfloat16*)k_cache,
                 (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, seg_start, seg_len, seg_kv_len,
                 block_tables, table_stride, num_segs, heads, kv_heads, page_size, page_shift, (int)cache_pages, window,
-                scale * LOG2E, error_word);
+                scale * LOG2E, error_word, keep_first, sink, (int)(sink.p != nullptr));
     return jllm_check_launch("attention_prefill_tc");
+}
+
+JLLM_EXPORT int jllm_attention_prefill_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                          long long cache_pages, void* out, int out_stride, const int* seg_start,
+                                          const int* seg_len, const int* seg_kv_len, const int* block_tables,
+                                          int table_stride, int num_segs, int rows, int heads, int kv_heads,
+                                          int head_dim, int page_size, int window, float scale, cudaStream_t stream) {
+    return prefill_tc_any(q, q_stride, k_cache, v_cache, cache_pages, out, out_stride, seg_start, seg_len, seg_kv_len, block_tables,
+                          table_stride, num_segs, rows, heads, kv_heads, head_dim, page_size, window, scale, stream, 0,
+                          VecRef{nullptr, JLLM_F32});
+}
+
+// The same with a window that keeps the request's first `keep_first` keys visible and / or a sink per query head.
+JLLM_EXPORT int jllm_attention_prefill_tc_extras(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                                 long long cache_pages, void* out, int out_stride, const int* seg_start,
+                                                 const int* seg_len, const int* seg_kv_len, const int* block_tables,
+                                                 int table_stride, int num_segs, int rows, int heads, int kv_heads,
+                                                 int head_dim, int page_size, int window, float scale, int keep_first,
+                                                 const void* sink, int sink_dtype, cudaStream_t stream) {
+    return prefill_tc_any(q, q_stride, k_cache, v_cache, cache_pages, out, out_stride, seg_start, seg_len, seg_kv_len, block_tables,
+                          table_stride, num_segs, rows, heads, kv_heads, head_dim, page_size, window, scale, stream, keep_first,
+                          VecRef{sink, sink_dtype});
 }

@@ -151,6 +151,16 @@ __host__ __device__ __forceinline__ int jllm_first_key(int P, int window) {
     return window > 0 ? (P + 1 - window > 0 ? P + 1 - window : 0) : (window < 0 ? P - P % (-window) : 0);
 }
 
+// With a window, a request's first `keep` keys may stay visible to every later row (`keep` 0: none): a row at P sees the
+// keys [0, min(keep, first)) and [first, P]. The kernels that take this walk a row's visible keys by an index u that counts
+// them in ascending order: u < kept is key u, u >= kept is key first + (u - kept), with kept = jllm_kept_keys(first, keep).
+__host__ __device__ __forceinline__ int jllm_kept_keys(int first, int window, int keep) {
+    return window > 0 && keep > 0 ? (keep < first ? keep : first) : 0;
+}
+__host__ __device__ __forceinline__ bool jllm_key_visible(int key, int P, int first, int keep) {
+    return key <= P && (key >= first || key < keep);
+}
+
 // ---- the gate of a gated feed-forward: act(gate) * up -----------------------------------------------------
 // `kind` is what the products' launchers take as their `swiglu` argument: 0 no gating, 1 silu (z / (1 + exp(-z))),
 // 2 the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) = z / (1 + exp(-2 u)) with u the tanh's

@@ -145,6 +145,9 @@ class _Signatures:
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_decode_flat = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    jllm_attention_decode_extras = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P, I, P]
+    jllm_attention_prefill_extras = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, I, P]
+    jllm_attention_prefill_tc_extras = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, I, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc_error = []
@@ -1040,9 +1043,29 @@ def decode_bucket_cap(rows, kv_heads, heads, head_dim, window, scratch, places: 
     return cap
 
 
+def attention_decode_extras(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads, head_dim,
+                            page_size, window, scale, splits=1, scratch=None, keep_first: int = 0, sink=None) -> None:
+    """`attention_decode` with a window that keeps the request's first `keep_first` keys visible and / or a sink per query
+    head: the general kernel for every head size (a row's visible keys are walked by an index that counts them), the sink
+    added where a row's parts meet."""
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and \
+            scratch.numel() >= attention_decode_scratch_floats(rows, heads, head_dim, splits)
+    global launch_count
+    launch_count += 1 if splits > 1 else 0
+    _call("jllm_attention_decode_extras", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+          rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(splits), _p(scratch), int(keep_first),
+          _p(sink), _DT[sink.dtype] if sink is not None else F32, _stream())
+
+
 def _attention_decode_rows(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim, page_size,
-                           window, scale, kv_bucket, scratch):
+                           window, scale, kv_bucket, scratch, keep_first: int = 0, sink=None):
     bucket = _windowed_bucket(kv_bucket, window)
+    if keep_first or sink is not None:
+        splits = decode_splits(rows, kv_heads, bucket, heads, head_dim, scratch)
+        return attention_decode_extras(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim,
+                                       page_size, window, scale, splits, scratch, keep_first, sink)
     how, n = decode_plan(rows, kv_heads, bucket, heads, head_dim, scratch)
     if how == "flat":
         return attention_decode_flat(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim,
@@ -1099,12 +1122,16 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
     """Causal attention of every row of the batch over its own request's cached keys and values. `window`: 0 every
     earlier key, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions (position p lies in chunk
     p // c). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
-    of one width only, so such a mixer runs on the plain kernel."""
-    one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim and not keep_first and sink is None
+    of one width only, so such a mixer runs on the plain kernel. `keep_first` (with a window): the request's first keys stay
+    visible to every row. `sink` [heads]: a number per query head whose exponential joins the softmax's denominator. With
+    either, single rows run on the general decode kernel and prompt portions on the tcgen05 kernel of one query tile (heads of
+    128) or the mma.sync kernel (64, 256)."""
+    one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim
+    extras = bool(keep_first) or sink is not None
     if one_width and batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
         return _attention_decode_rows(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                       batch.rows, heads, kv_heads, head_dim, page_size, window, scale, batch.kv_bucket,
-                                      scratch)
+                                      scratch, keep_first, sink)
     if one_width and q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
         # prompt portions through the flash kernel; the single rows riding beside them (the scheduler puts them
         # last) through the decode kernel, which shares every key among the query heads of a kv head
@@ -1114,20 +1141,20 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
         if mr > 0:
             attention_prefill(q[:mr], k_cache, v_cache, out[:mr], batch.seg_start[:ms], batch.seg_len[:ms],
                               batch.seg_kv_len[:ms], batch.block_tables[group], mr, heads, kv_heads, head_dim, page_size,
-                              window, scale)
+                              window, scale, keep_first=keep_first, sink=sink)
         if mr < batch.rows:
             n = batch.rows - mr
             _attention_decode_rows(q[mr:], k_cache, v_cache, out[mr:], batch.row_seg[mr:], batch.positions[mr:],
                                    batch.block_tables[group], n, heads, kv_heads, head_dim, page_size, window, scale,
-                                   batch.kv_bucket, scratch)
+                                   batch.kv_bucket, scratch, keep_first, sink)
         return
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale, value_dim, keep_first, sink)
 
 
 def attention_tiles_take(keep_first: int, sink) -> bool:
-    """Whether the tile kernels (decode, prompt) take an attention with these extras; the plain kernel takes all."""
-    return not keep_first and sink is None
+    """Whether the tile kernels (decode, prompt) take an attention with these extras (they do; the plain kernel takes all)."""
+    return True
 
 
 def attention_prefill_fits(head_dim) -> bool:
@@ -1144,7 +1171,7 @@ def attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size) -> bool:
 
 
 def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, block_tables, rows, heads, kv_heads,
-                      head_dim, page_size, window, scale, kernel: str = "auto") -> None:
+                      head_dim, page_size, window, scale, kernel: str = "auto", keep_first: int = 0, sink=None) -> None:
     """Flash attention of prompt portions: segments of consecutive rows, each over its own request's pages.
     Head size 128 runs on tcgen05 (both products, accumulators in tensor memory; kernel "pair" or "tc"), other
     sizes on mma.sync ("mma")."""
@@ -1152,6 +1179,19 @@ def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, 
         # two query tiles per block where the portions are long enough to fill them (the tiles take turns on the
         # tensor cores); one tile per block, with two S buffers, for short portions
         kernel = "pair" if rows > 128 * seg_start.numel() and PREFILL_TC != 3 else "tc"
+    if keep_first or sink is not None:
+        # kept first keys and a sink: the tcgen05 kernel of one query tile per block, or the mma.sync kernel
+        kernel = "tc" if kernel in ("tc", "pair") else "mma"
+        sd = _DT[sink.dtype] if sink is not None else F32
+        if kernel == "tc":
+            return _call("jllm_attention_prefill_tc_extras", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                         k_cache.shape[0], out.data_ptr(), out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(),
+                         seg_kv_len.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), seg_start.numel(), rows,
+                         heads, kv_heads, head_dim, page_size, int(window), float(scale), int(keep_first), _p(sink), sd, _stream())
+        return _call("jllm_attention_prefill_extras", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                     out.data_ptr(), out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_kv_len.data_ptr(),
+                     block_tables.data_ptr(), block_tables.stride(0), seg_start.numel(), rows, heads, kv_heads, head_dim,
+                     page_size, int(window), float(scale), int(keep_first), _p(sink), sd, _stream())
     if kernel in ("tc", "pair"):
         return _call("jllm_attention_prefill_tc" if kernel == "tc" else "jllm_attention_prefill_pair", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                      k_cache.shape[0], out.data_ptr(), out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(),

@@ -177,6 +177,45 @@ def test_a_single_key_that_stands_out_at_every_edge(where, decoding):
     assert near == sees, f"{where}: the row {'sees' if sees else 'must not see'} key {key}"
 
 
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("H, G, hd, page, size, keep", [(4, 2, 128, 16, 70, 9), (6, 3, 64, 16, 200, 33), (2, 2, 48, 4, 16, 5), (16, 1, 256, 16, 129, 0),
+                                                        (4, 4, 32, 8, 1, 20), (3, 1, 96, 16, 0, 0)])
+def test_decode_attention_with_kept_tokens_and_a_sink(splits, H, G, hd, page, size, keep):
+    """Single rows through the general decode kernel, a row's keys split over several blocks: the kept tokens and the window
+    are one run of visible keys, and the sink joins once, where the parts meet."""
+    o = ops()
+    lens = [1, 70, 201, 37, 130, 420]
+    d, want = window_case(torch.bfloat16, H, G, hd, hd, page, lens, [1] * len(lens), size, keep, 1.0 / math.sqrt(hd), seed=hd + size)
+    rows = len(lens)
+    out = torch.zeros(rows, H * hd, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.zeros(o.attention_decode_scratch_floats(rows, H, hd, splits) + 1, device=DEV)
+    o.attention_decode_extras(d["q"], d["k"], d["v"], out, d["row_seg"], d["row_pos"], d["tables"], rows, H, G, hd, page, size,
+                              1.0 / math.sqrt(hd), splits, scratch, keep, d["sink"])
+    torch.cuda.synchronize()
+    close(out, want, torch.bfloat16, "decode", loose=2.0)
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("H, G, hd, page, size, keep", [(4, 2, 128, 16, 70, 9), (2, 1, 128, 8, 128, 140), (6, 3, 64, 16, 200, 33), (2, 2, 64, 4, 16, 5),
+                                                        (2, 1, 256, 16, 129, 64), (4, 2, 128, 16, 300, 0), (2, 2, 128, 16, 1, 200), (2, 1, 128, 16, 0, 0)])
+def test_prompt_attention_kernels_with_kept_tokens_and_a_sink(kernel, H, G, hd, page, size, keep):
+    """Prompt portions on top of cached keys through the tile kernels: the key tiles of the kept tokens are walked in front of
+    the window's, whole tiles and edge tiles of both kinds; portions of 1 to 333 rows."""
+    o = ops()
+    if kernel == "tc" and hd != 128:
+        pytest.skip("the tcgen05 prompt kernel takes heads of 128")
+    lens, q_lens = [1, 70, 420, 37, 600], [1, 70, 333, 20, 130]
+    d, want = window_case(torch.bfloat16, H, G, hd, hd, page, lens, q_lens, size, keep, 1.0 / math.sqrt(hd), seed=hd + size + keep)
+    rows = sum(q_lens)
+    starts = [sum(q_lens[:i]) for i in range(len(q_lens))]
+    out = torch.zeros(rows, H * hd, dtype=torch.bfloat16, device=DEV)
+    o.attention_prefill(d["q"], d["k"], d["v"], out, i32(starts), i32(q_lens), i32(lens), d["tables"], rows, H, G, hd, page, size,
+                        1.0 / math.sqrt(hd), kernel=kernel, keep_first=keep, sink=d["sink"])
+    torch.cuda.synchronize()
+    o.check_kernel_errors()
+    close(out, want, torch.bfloat16, f"prompt portions ({kernel})", loose=2.0)
+
+
 def test_the_sink_counts_once_and_is_not_scaled():
     """With one visible key the weight of its value is exp(s) / (exp(s) + exp(sink)): a sink of 0 beside a score of 0 halves
     it whatever the score multiplier; without the sink it is 1."""
