@@ -893,6 +893,262 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         }
 }
 
+// ---- the same chunks with a decay and an input scale per TOKEN (and head) ------------------------------------------------
+// S_t = a_t S_(t-1) + (b_t k_t) v_t^T, o_t = S_t^T (s q_t) [+ D v_t]: with cl_t the sum of log a over the chunk's tokens up to
+// t, a chunk is the same four products:
+//     P[t, s] = (q_t . k_s) s exp(cl_t - cl_s) b_s  for s <= t       o_t = sum_s P[t, s] v_s + exp(cl_t) s (q_t^T S0) [+ D v_t]
+//     S       = exp(cl_n) S0 + sum_s (b_s exp(cl_n - cl_s) k_s) v_s^T
+// Every exponent is a difference that is <= 0. The float32 factors meet float32 values (the scores behind their product, the
+// keys in front of theirs, the state in its registers) and become tensor-core operands as two bfloat16 values each, as above.
+// q and k may be shared by the heads of a group; the sources may be float32 (rounded to bfloat16 on their way into shared
+// memory: they are projections, the operands the products take) or bfloat16.
+__device__ __forceinline__ uint4 load8(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint4 load8(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    __nv_bfloat162 r0 = __floats2bfloat162_rn(a.x, a.y), r1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 r2 = __floats2bfloat162_rn(b.x, b.y), r3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 out;
+    out.x = *reinterpret_cast<uint32_t*>(&r0);
+    out.y = *reinterpret_cast<uint32_t*>(&r1);
+    out.z = *reinterpret_cast<uint32_t*>(&r2);
+    out.w = *reinterpret_cast<uint32_t*>(&r3);
+    return out;
+}
+
+template <typename TS, int DK, int DVB>
+__global__ void __launch_bounds__(256)
+gated_chunk_kernel(const TS* __restrict__ qp, int ld_q, int q_off, int q_groups, const TS* __restrict__ kp, int ld_k, int k_off,
+                   int k_groups, const TS* __restrict__ vp, int ld_v, int v_off, const float* __restrict__ la,
+                   const float* __restrict__ bsc, VecRef skip, int has_skip, float* __restrict__ state,
+                   const int* __restrict__ seg_start, const int* __restrict__ seg_len, const int* __restrict__ state_slots,
+                   float* __restrict__ o, int heads, int dv, int num_slots, float q_scale) {
+    constexpr int LDQ = DK + 8;
+    constexpr int OT = DVB / 16;
+    constexpr int ST = DVB / 16;
+    constexpr int SPARTS = 8 / ST;
+    constexpr int NS = DK / SPARTS / 8;
+    extern __shared__ __align__(16) unsigned char lightning_smem[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lightning_smem);   // [C][LDQ]     q
+    __nv_bfloat16* Ks = Qs + C * LDQ;                                       // [C][LDQ]     k
+    __nv_bfloat16* Vt = Ks + C * LDQ;                                       // [DVB][LDC]   v, transposed
+    __nv_bfloat16* Kh = Vt + DVB * LDC;                                     // [DK][LDC]    weighted k, transposed: value
+    __nv_bfloat16* Kl = Kh + DK * LDC;                                      //              ... and what its rounding left
+    __nv_bfloat16* Ph = Kl + DK * LDC;                                      // [C][LDC]     P
+    __nv_bfloat16* Pl = Ph + C * LDC;
+    __nv_bfloat16* Sh = Pl + C * LDC;                                       // [DVB][LDQ]   the state, transposed
+    __nv_bfloat16* Sl = Sh + DVB * LDQ;
+    float* cl = reinterpret_cast<float*>(Sl + DVB * LDQ);                   // [C]  the chunk's log decays, summed up to each token
+    float* bs = cl + C;                                                     // [C]  its input scales (0 past the chunk's end)
+    pdl_wait();
+    pdl_trigger();
+    const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DVB;
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mt = w & 3, half = w >> 2, smt = w % ST, spart = w / ST;
+    const int first = seg_start[seg], n = seg_len[seg], slot = state_slots[seg];
+    if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
+    const int qg = h / (heads / q_groups), kg = h / (heads / k_groups);
+    float* S = state + (((size_t)slot * heads + h) * DK) * dv;
+    const float d_skip = has_skip ? skip[h] : 0.f;
+    float sacc[NS][4];
+    const int vrow = smt * 16 + g, kcol0 = spart * (DK / SPARTS) + 2 * t;
+#pragma unroll
+    for (int j = 0; j < NS; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = c0 + vrow + (e >> 1) * 8, ch = kcol0 + j * 8 + (e & 1);
+            sacc[j][e] = col < dv ? S[(size_t)ch * dv + col] : 0.f;
+        }
+    auto park_state = [&]() {
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+            const int ch = kcol0 + j * 8;
+            store_split2(Sh + (size_t)vrow * LDQ + ch, Sl + (size_t)vrow * LDQ + ch, sacc[j][0], sacc[j][1]);
+            store_split2(Sh + (size_t)(vrow + 8) * LDQ + ch, Sl + (size_t)(vrow + 8) * LDQ + ch, sacc[j][2], sacc[j][3]);
+        }
+    };
+    park_state();
+    const size_t row_o = (size_t)heads * dv;
+    constexpr int QI = C * (DK / 8) / 256, VI = C * (DVB / 8) / 256;
+    uint4 fq[QI], fk[QI], fv[VI];
+    float fla = 0.f, fb = 0.f;              // this thread's token's gates (threads below C), a chunk ahead like q, k and v
+    auto fetch = [&](int t0) {
+        const int nt = min(C, n - t0);
+#pragma unroll
+        for (int u = 0; u < QI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            fq[u] = fk[u] = make_uint4(0, 0, 0, 0);
+            if (srow < nt) {
+                const size_t r = (size_t)(first + t0 + srow);
+                fq[u] = load8(qp + r * ld_q + q_off + (size_t)qg * DK + piece * 8);
+                fk[u] = load8(kp + r * ld_k + k_off + (size_t)kg * DK + piece * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            fv[u] = make_uint4(0, 0, 0, 0);
+            if (srow < nt && c0 + piece * 8 < dv)
+                fv[u] = load8(vp + (size_t)(first + t0 + srow) * ld_v + v_off + (size_t)h * dv + c0 + piece * 8);
+        }
+        if (tid < C) {
+            fla = 0.f;
+            fb = 0.f;
+            if (tid < nt) {
+                fla = la[(size_t)(first + t0 + tid) * heads + h];
+                fb = bsc[(size_t)(first + t0 + tid) * heads + h];
+            }
+        }
+    };
+    if (n > 0) fetch(0);
+    for (int t0 = 0; t0 < n; t0 += C) {
+        const int nt = min(C, n - t0);
+        __syncthreads();       // the parked state is written; the tiles and gates of the chunk before are no longer read
+        // ---- the chunk's gates: log decays summed up to each token (two warps scan 32 tokens each, the second adds the
+        //      first's total), input scales ----
+        if (tid < C) {
+            float v = fla;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += up;
+            }
+            cl[tid] = v;
+            bs[tid] = fb;
+        }
+        __syncthreads();
+        if (tid >= 32 && tid < C) cl[tid] += cl[31];
+        __syncthreads();
+        const float cl_end = cl[nt - 1];
+#pragma unroll
+        for (int u = 0; u < QI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            *reinterpret_cast<uint4*>(Qs + (size_t)srow * LDQ + piece * 8) = fq[u];
+            *reinterpret_cast<uint4*>(Ks + (size_t)srow * LDQ + piece * 8) = fk[u];
+            const float wgt = srow < nt ? __fmul_rn(bs[srow], expf(cl_end - cl[srow])) : 0.f;
+            const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(&fk[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat16 hi, lo;
+                split(__bfloat162float(kv[i]) * wgt, hi, lo);
+                Kh[(size_t)(piece * 8 + i) * LDC + srow] = hi;
+                Kl[(size_t)(piece * 8 + i) * LDC + srow] = lo;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            const __nv_bfloat16* vv = reinterpret_cast<const __nv_bfloat16*>(&fv[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) Vt[(size_t)(piece * 8 + i) * LDC + srow] = vv[i];
+        }
+        if (t0 + C < n) fetch(t0 + C);
+        __syncthreads();
+        // ---- P = q k^T for this warp's 16 tokens and 32 keys, times the decays between key and token and the key's scale ----
+        float acc[4][4] = {};
+        float o2[OT][4] = {};
+        for (int k0 = 0; k0 < DK; k0 += 16) {
+            uint32_t a[4];
+            load_a(a, Qs, LDQ, mt * 16, k0, lane);
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Ks, LDQ, half * 32 + j * 8, k0, lane);
+                mma_bf16(acc[j], a, b[0], b[1]);
+                mma_bf16(acc[j + 1], a, b[2], b[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < OT; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Sh, LDQ, half * (DVB / 2) + j * 8, k0, lane);
+                mma_bf16(o2[j], a, b[0], b[1]);
+                mma_bf16(o2[j + 1], a, b[2], b[3]);
+                load_b2(b, Sl, LDQ, half * (DVB / 2) + j * 8, k0, lane);
+                mma_bf16(o2[j], a, b[0], b[1]);
+                mma_bf16(o2[j + 1], a, b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int key = half * 32 + j * 8 + 2 * t;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int tok = mt * 16 + g + hrow * 8;
+                const float ct = cl[tok];
+                const float p0 = key <= tok ? __fmul_rn(__fmul_rn(acc[j][2 * hrow], q_scale), __fmul_rn(expf(ct - cl[key]), bs[key])) : 0.f;
+                const float p1 = key + 1 <= tok
+                                     ? __fmul_rn(__fmul_rn(acc[j][2 * hrow + 1], q_scale), __fmul_rn(expf(ct - cl[key + 1]), bs[key + 1])) : 0.f;
+                store_split2(Ph + (size_t)tok * LDC + key, Pl + (size_t)tok * LDC + key, p0, p1);
+            }
+        }
+        __syncthreads();
+        // ---- o = P v + exp(cl_t) s q^T S0 [+ D v] ----
+        float o1[OT][4] = {};
+        for (int k0 = 0; k0 < C; k0 += 16) {
+            uint32_t ah[4], al[4];
+            load_a(ah, Ph, LDC, mt * 16, k0, lane);
+            load_a(al, Pl, LDC, mt * 16, k0, lane);
+#pragma unroll
+            for (int j = 0; j < OT; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Vt, LDC, half * (DVB / 2) + j * 8, k0, lane);
+                mma_bf16(o1[j], ah, b[0], b[1]);
+                mma_bf16(o1[j], al, b[0], b[1]);
+                mma_bf16(o1[j + 1], ah, b[2], b[3]);
+                mma_bf16(o1[j + 1], al, b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < OT; ++j) {
+            const int lcol = half * (DVB / 2) + j * 8 + 2 * t, col = c0 + lcol;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int tok = mt * 16 + g + hrow * 8;
+                if (tok < nt && col < dv) {
+                    const float f = __fmul_rn(expf(cl[tok]), q_scale);
+                    float* dst = o + (size_t)(first + t0 + tok) * row_o + (size_t)h * dv + col;
+                    float r0 = __fadd_rn(o1[j][2 * hrow], __fmul_rn(f, o2[j][2 * hrow]));
+                    float r1 = __fadd_rn(o1[j][2 * hrow + 1], __fmul_rn(f, o2[j][2 * hrow + 1]));
+                    if (has_skip) {
+                        r0 = fmaf(d_skip, __bfloat162float(Vt[(size_t)lcol * LDC + tok]), r0);
+                        r1 = fmaf(d_skip, __bfloat162float(Vt[(size_t)(lcol + 1) * LDC + tok]), r1);
+                    }
+                    dst[0] = r0;
+                    if (col + 1 < dv) dst[1] = r1;
+                }
+            }
+        }
+        // ---- S = exp(cl_n) S0 + v^T (weighted k) ----
+        const float dn = expf(cl_end);
+#pragma unroll
+        for (int j = 0; j < NS; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[j][e] = __fmul_rn(sacc[j][e], dn);
+        for (int k0 = 0; k0 < C; k0 += 16) {
+            uint32_t a[4];
+            load_a(a, Vt, LDC, smt * 16, k0, lane);
+#pragma unroll
+            for (int j = 0; j < NS; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Kh, LDC, spart * (DK / SPARTS) + j * 8, k0, lane);
+                mma_bf16(sacc[j], a, b[0], b[1]);
+                mma_bf16(sacc[j + 1], a, b[2], b[3]);
+                load_b2(b, Kl, LDC, spart * (DK / SPARTS) + j * 8, k0, lane);
+                mma_bf16(sacc[j], a, b[0], b[1]);
+                mma_bf16(sacc[j + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+        park_state();
+    }
+#pragma unroll
+    for (int j = 0; j < NS; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = c0 + vrow + (e >> 1) * 8, ch = kcol0 + j * 8 + (e & 1);
+            if (col < dv) S[(size_t)ch * dv + col] = sacc[j][e];
+        }
+}
+
 template <int DK, int DVB>
 constexpr size_t smem_bytes() {
     return (size_t)(2 * C * (DK + 8) + DVB * LDC + 2 * DK * LDC + 2 * C * LDC + 2 * DVB * (DK + 8)) * sizeof(__nv_bfloat16) +
@@ -1085,4 +1341,46 @@ JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype
         jllm_launch(gated_head_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
                     (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, rows, heads, dv, eps, scale, gate_kind);
     return jllm_check_launch("gated_head_norm");
+}
+
+
+// The recurrence with a decay and an input scale per token and head (`jllm_scalar_gated_recurrent`, which this stands in for
+// where a step holds prompt portions) in chunks of 64 tokens on the tensor cores: key heads of 64 or 128 channels, no
+// normalizer. q, k, v: views of type `dtype` (float32 or bfloat16) with 16-byte aligned rows and pieces. Returns
+// JLLM_UNSUPPORTED without launching where the shape is not taken (the caller then runs token by token).
+JLLM_EXPORT int jllm_scalar_gated_chunked(const void* q, int ld_q, int q_off, int q_groups, const void* k, int ld_k, int k_off,
+                                          int k_groups, const void* v, int ld_v, int v_off, int dtype, const float* la,
+                                          const float* b, const void* skip, int skip_dtype, float* state, int num_slots,
+                                          const int* seg_start, const int* seg_len, const int* state_slots, float* o,
+                                          int segments, int heads, int dk, int dv, float q_scale, cudaStream_t stream) {
+    const int per = dtype == JLLM_F32 ? 4 : 8;          // values of a 16-byte piece
+    const bool aligned = ld_q % per == 0 && ld_k % per == 0 && ld_v % per == 0 && q_off % per == 0 && k_off % per == 0 &&
+                         v_off % per == 0 && dv % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 &&
+                         ((uintptr_t)v % 16) == 0;
+    if (!(dk == 64 || dk == 128) || !aligned || heads % q_groups || heads % k_groups || heads > 65535) return JLLM_UNSUPPORTED;
+    if (segments == 0) return JLLM_OK;
+    const VecRef sk{skip, skip_dtype};
+    const int has_skip = skip != nullptr;
+    const long long sms = max(1, jllm_device_sm_count());
+    const bool wide = g_lightning_width ? g_lightning_width == 64 : (long long)segments * heads * ((dv + 63) / 64) >= sms;
+#define JLLM_GATED_CHUNK(TS, DK, DVB)                                                                                          \
+    do {                                                                                                                        \
+        auto kernel = lightning::gated_chunk_kernel<TS, DK, DVB>;                                                               \
+        const size_t smem = lightning::smem_bytes<DK, DVB>() + 2 * lightning::C * sizeof(float);                                \
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)                \
+            return jllm_fail(JLLM_CUDA_ERROR, "gated_chunk: %zu bytes of shared memory refused", smem);                         \
+        jllm_launch(kernel, dim3(segments, heads, (dv + DVB - 1) / DVB), dim3(256), smem, stream, LAUNCH_DEPENDENT,             \
+                    (const TS*)q, ld_q, q_off, q_groups, (const TS*)k, ld_k, k_off, k_groups, (const TS*)v, ld_v, v_off, la, b, \
+                    sk, has_skip, state, seg_start, seg_len, state_slots, o, heads, dv, num_slots, q_scale);                    \
+        return jllm_check_launch("gated_chunk");                                                                                \
+    } while (0)
+    if (dtype == JLLM_F32) {
+        if (dk == 64) { if (wide) JLLM_GATED_CHUNK(float, 64, 64); JLLM_GATED_CHUNK(float, 64, 32); }
+        if (wide) JLLM_GATED_CHUNK(float, 128, 64);
+        JLLM_GATED_CHUNK(float, 128, 32);
+    }
+    if (dk == 64) { if (wide) JLLM_GATED_CHUNK(__nv_bfloat16, 64, 64); JLLM_GATED_CHUNK(__nv_bfloat16, 64, 32); }
+    if (wide) JLLM_GATED_CHUNK(__nv_bfloat16, 128, 64);
+    JLLM_GATED_CHUNK(__nv_bfloat16, 128, 32);
+#undef JLLM_GATED_CHUNK
 }

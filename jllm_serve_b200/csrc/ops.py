@@ -186,6 +186,7 @@ class _Signatures:
     jllm_memory_gates = [P, I, I, I, P, P, I, F, P, I, P, P, P, P, P, P, I, I, P]
     jllm_causal_conv = [P, I, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_scalar_gated_recurrent = [P, I, I, I, P, I, I, I, P, I, I, I, P, P, P, P, I, P, P, I, P, P, P, P, I, I, I, I, F, P]
+    jllm_scalar_gated_chunked = [P, I, I, I, P, I, I, I, P, I, I, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, P]
     jllm_sigmoid_gate = [P, I, P, I, I, I, I, F, P]
     jllm_activation = [P, I, ctypes.c_longlong, I, P]
     jllm_add_rows_scaled = [P, P, I, I, P, I, I, I, P]
@@ -508,6 +509,34 @@ def scalar_gated_recurrent(q, q_off, q_groups, k, k_off, k_groups, v, v_off, log
           in_scale.data_ptr(), _p(floor), _p(skip), _DT[skip.dtype] if skip is not None else F32, state.data_ptr(),
           _p(normalizer), state.shape[0], batch.seg_start.data_ptr(), batch.seg_len.data_ptr(), batch.state_slots.data_ptr(),
           out.data_ptr(), batch.seg_start.numel(), int(heads), int(key_dim), int(value_dim), float(query_scale), _stream())
+
+
+GATED_CHUNKS = int(os.environ.get("JLLM_B200_GATED_CHUNKS", "1"))      # 0: prompt portions token by token everywhere
+
+
+def scalar_gated_chunked(q, q_off, q_groups, k, k_off, k_groups, v, v_off, log_decay, in_scale, state, batch, out, heads,
+                         key_dim, value_dim, query_scale: float = 1.0, skip=None) -> bool:
+    """`scalar_gated_recurrent` (without a normalizer) for steps that hold prompt portions, in chunks of 64 tokens on the
+    tensor cores: q, k, v enter as bfloat16 operands (float32 sources are rounded on their way in), the decays and scales are
+    applied in float32 and every float32 factor becomes two bfloat16 operands. Key heads of 64 or 128 channels and 16-byte
+    aligned pieces; says False, having launched nothing, where the shape is not taken."""
+    if not GATED_CHUNKS or key_dim not in (64, 128):
+        return False
+    assert q.dtype == k.dtype == v.dtype and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert state.dtype == out.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous()
+    fn = library().jllm_scalar_gated_chunked
+    code = fn(q.data_ptr(), q.stride(0), int(q_off), int(q_groups), k.data_ptr(), k.stride(0), int(k_off), int(k_groups),
+              v.data_ptr(), v.stride(0), int(v_off), _DT[q.dtype], log_decay.data_ptr(), in_scale.data_ptr(), _p(skip),
+              _DT[skip.dtype] if skip is not None else F32, state.data_ptr(), state.shape[0], batch.seg_start.data_ptr(),
+              batch.seg_len.data_ptr(), batch.state_slots.data_ptr(), out.data_ptr(), batch.seg_start.numel(), int(heads),
+              int(key_dim), int(value_dim), float(query_scale), _stream())
+    if code == 3:        # the library's word for "this shape is not taken"
+        return False
+    if code != 0:
+        raise KernelError(f"jllm_scalar_gated_chunked failed ({code}): {library().jllm_last_error().decode(errors='replace')}")
+    global launch_count
+    launch_count += 1
+    return True
 
 
 def sigmoid_gate(y, gate, scale: float = 1.0) -> None:

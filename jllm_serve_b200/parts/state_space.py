@@ -69,9 +69,15 @@ class SelectiveStateSpace(Mixer):
         b = self.rt.buffer("recurrence_in_scale", H, torch.float32)[:rows]
         ops.ssm_gates(proj[:, inner + C:inner + C + H], self.dt_bias, self.a_log, la, b)
         y = self.rt.buffer("ssm_out", inner, torch.float32)[:rows]
-        # keys B at column inner, queries C at inner + G N, values x at 0 of the convolution's result
-        ops.scalar_gated_recurrent(mixed, inner + G * N, G, mixed, inner, G, mixed, 0, la, b, cache.states[0], batch, y, H, N, P,
-                                   1.0, skip=self.skip)
+        # keys B at column inner, queries C at inner + G N, values x at 0 of the convolution's result. Prompt portions in
+        # bfloat16 mode with states of 64 or 128 values go through the tensor cores in chunks of 64 tokens; everything else
+        # (single rows, float32 mode, other sizes) token by token
+        chunked = (not batch.decode_only and self.rt.dtype == torch.bfloat16 and
+                   ops.scalar_gated_chunked(mixed, inner + G * N, G, mixed, inner, G, mixed, 0, la, b, cache.states[0], batch, y, H, N,
+                                            P, 1.0, skip=self.skip))
+        if not chunked:
+            ops.scalar_gated_recurrent(mixed, inner + G * N, G, mixed, inner, G, mixed, 0, la, b, cache.states[0], batch, y, H, N,
+                                       P, 1.0, skip=self.skip)
         gated = self.rt.buffer("ssm_gated", inner)[:rows]
         ops.gated_head_norm(y, proj[:, :inner], self.gain, s.norm_eps, self.out_scale, gated, s.norm_groups, inner // s.norm_groups,
                             "silu", gate_first=True, gain_per_column=True)

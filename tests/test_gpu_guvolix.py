@@ -373,6 +373,61 @@ def test_the_recurrence_over_segments_slots_and_portions(dtype, H, G, dk, dv, fo
     assert float(state[1].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("src", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block_width", [32, 64])
+@pytest.mark.parametrize("H, G, dk, dv", [(4, 2, 64, 64), (2, 1, 128, 40), (3, 3, 64, 128), (8, 2, 128, 64)])
+def test_the_recurrence_in_chunks_on_the_tensor_cores(H, G, dk, dv, block_width, src):
+    """Prompt portions of 1 to 300 rows on top of states that earlier steps left, then single rows token by token: the chunk
+    kernel against the float64 recurrence over operands rounded to bfloat16 (what its products take); strong decays (a chunk's
+    product far below the smallest float) and none at all; keys and queries shared by the heads of a group; the skip."""
+    o = ops()
+    g = torch.Generator().manual_seed(H * dk + dv)
+    lens = [300, 70, 1]
+    data = []
+    for n in lens:
+        q, k = torch.randn(n, G, dk, generator=g), torch.randn(n, G, dk, generator=g) / math.sqrt(dk)
+        v = torch.randn(n, H, dv, generator=g)
+        la = -torch.rand(n, H, generator=g) * torch.tensor([0.01, 0.5, 3.0, 0.0][:H] + [0.2] * max(0, H - 4))
+        b = torch.rand(n, H, generator=g) * 1.5
+        q, k, v = q.bfloat16().float(), k.bfloat16().float(), v.bfloat16().float()
+        data.append((q, k, v, la, b))
+    skip = torch.randn(H, generator=g)
+    want = []
+    for q, k, v, la, b in data:
+        S = torch.zeros(H, dk, dv, dtype=torch.float64)
+        want.append(plain_recurrence(q.double().repeat_interleave(H // G, 1), k.double().repeat_interleave(H // G, 1), v.double(),
+                                     la.double(), b.double(), S, skip=skip.double(), q_scale=0.5))
+    state = torch.zeros(4, H, dk, dv, device=DEV)
+    got = [torch.zeros(n, H * dv) for n in lens]
+    cuts = [[(0, 130), (130, 299), (299, 300)], [(0, 64), (64, 70)], [(0, 1)]]
+    o.lightning_block_width(block_width)
+    try:
+        for step in range(3):
+            segs = [(s, *cuts[s][step]) for s in range(3) if step < len(cuts[s])]
+            cat = lambda i, w: torch.cat([data[s][i][lo:hi].reshape(hi - lo, w) for s, lo, hi in segs])
+            buf = torch.cat([torch.zeros(sum(hi - lo for _, lo, hi in segs), 8), cat(0, G * dk), cat(1, G * dk), cat(2, H * dv)], dim=1)
+            buf = buf.to(DEV, src)
+            batch = FakeBatch([hi - lo for _, lo, hi in segs], [3 - s for s, _, _ in segs])
+            la, b = (cat(i, H).to(DEV).contiguous() for i in (3, 4))
+            out = torch.zeros(buf.shape[0], H * dv, device=DEV)
+            args = (buf, 8, G, buf, 8 + G * dk, G, buf, 8 + 2 * G * dk, la, b, state, batch, out, H, dk, dv, 0.5)
+            if batch.decode_only:
+                o.scalar_gated_recurrent(*args, skip=skip.to(DEV))
+            else:
+                assert o.scalar_gated_chunked(*args, skip=skip.to(DEV))
+            at = 0
+            for s, lo, hi in segs:
+                got[s][lo:hi] = out[at:at + hi - lo].cpu()
+                at += hi - lo
+    finally:
+        o.lightning_block_width(0)
+    o.check_kernel_errors()
+    for s in range(3):
+        # (every float32 factor enters the products with 16 bits of mantissa)
+        close(got[s], want[s].reshape(lens[s], H * dv), torch.float32, f"request {s}", loose=5)
+    assert float(state[0].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("groups, width", [(2, 24), (1, 40), (3, 700), (5, 7)])
 def test_gate_in_front_of_a_norm_in_parts_and_a_gain_per_column(dtype, groups, width):
@@ -505,7 +560,8 @@ class Checker:
             allowed, cap = max(3, 5 * len(self.errors) // 100), float("inf")
         assert len(over) <= allowed and worst[0] <= cap, \
             f"{self.what}: {len(over)} rows beyond {tol:.3e}, the first at {first}, the largest {worst}"
-        assert rms <= 3 * RMS_TOL[self.dtype] and 1 - self.flips / len(self.errors) >= ARGMAX_SHARE[self.dtype] - 0.04
+        wide = 3 if self.drawn and self.dtype == "bfloat16" else 1      # (the turned rows weigh in these sums too)
+        assert rms <= 3 * wide * RMS_TOL[self.dtype] and 1 - self.flips / len(self.errors) >= ARGMAX_SHARE[self.dtype] - 0.04 * wide
 
 
 def run_trace(name, dtype, steps, sequences, what, **kw):
