@@ -13,11 +13,13 @@ read (every weight once plus the cache of the live requests) with the measured c
 `points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
 layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
 
-`--design madevik`, `--design movivik` and `--design bozevik` are another program under the same roof and leave the default
+`--design madevik`, `--design movivik`, `--design bozevik` and `--design guvolix` are another program under the same roof and leave the default
 workload alone: prefill and decode of the Madevik design (gated linear attention, attention over a cached latent, routed
 experts), of the Movivik design (chunked and parallel attention layers, linear attention with fixed decays, norms in front of
 and behind every part) or of the Bozevik design (attention over a cached latent with a query latent and a shared rotated key
-part, layer norms behind the parts, token shift, depth mix, clamped gated units) at layer sizes that resemble a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
+part, layer norms behind the parts, token shift, depth mix, clamped gated units) or of the Guvolix design (one norm per
+layer that feeds an attention with a sink and kept first tokens beside a selective state space or a matrix memory, and a
+dense or routed feed-forward) at layer sizes that resemble a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
 picks among them); one JSON line with both models' figures per size.
 
 The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
@@ -166,6 +168,43 @@ def madevik_latent_shape(width, heads, rank, experts, top, ff, runs, vocab=32768
             "layers": [latent for _ in range(runs)]}
 
 
+def guvolix_shape(width, heads, kv_heads, ff, runs, window=1024, keep=64, vocab=32768):
+    """Layers in fours: three whose attention (a window with kept first tokens, a sink, a gate of full width) runs beside a
+    selective state space (inner width twice the model's, heads of 64 values, states of 128, eight groups), one whose attention
+    (a window, banded rotary scaling) runs beside a matrix memory (heads of 128 key and 256 value channels); attention heads of
+    128 throughout; a dense erf-GELU feed-forward and routed experts (softmax scores, two identity entries, a gated shared
+    expert) take turns."""
+    def left(p2):
+        rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0}}
+        mask = {"size": window, "keep_first": keep}
+        if p2:
+            rot = {"base": 20000.0, "dims": 128, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 4096}}
+            mask = {"size": window}
+        return {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot, "mask": mask}
+    ssm = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+    mem = {"heads": width // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 8, "top": 2, "identity": 2}, "shared": {"ff": ff // 8}}
+    layers = []
+    for i in range(runs):
+        mlp = moe if i % 2 else dense
+        if i % 4 == 3:
+            layers.append({"type": "parallel_2", "mlp": mlp,
+                           "mixer": {"left": left(True), "right": mem, "left_scale": 0.6, "right_scale": 1.1}})
+        else:
+            layers.append({"type": "parallel", "mlp": mlp, "mixer": {"left": left(False), "right": ssm}})
+    return {"architecture": "Guvolix", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
+            "layers": layers}
+
+
+def movivik_parallel_shape(width, heads, kv_heads, ff, runs, vocab=32768):
+    """A Movivik model of parallel layers only (the closest kin of the Guvolix shape): a causal attention beside linear
+    attention with a fixed decay per head, heads of 128, a dense gated feed-forward."""
+    cfg = movivik_shape(width, heads, kv_heads, ff, runs, vocab=vocab)
+    par = [l for l in cfg["layers"] if l["type"] == "parallel"][0]
+    return dict(cfg, layers=[par for _ in range(runs)])
+
+
 def _qwen3_shape(width, layers, heads, kv_heads, ffn):
     return dict(QWEN3_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
                 intermediate_size=ffn, vocab_size=32768)
@@ -184,6 +223,11 @@ DESIGN_SIZES = {
                           madevik_latent_shape(2048, 16, 256, 8, 2, 1024, 8), "madevik_latent"),
                 "w4096": (bozevik_shape(4096, 32, 96, 32, 1536, 16, 4, 768, 12288, 4), _qwen3_shape(4096, 4, 32, 8, 12288),
                           madevik_latent_shape(4096, 32, 128, 16, 4, 768, 4), "madevik_latent")},
+    # beside each the Qwen3 shape and a Movivik model of parallel layers (attention beside linear attention)
+    "guvolix": {"w2048": (guvolix_shape(2048, 16, 8, 8192, 8), _qwen3_shape(2048, 8, 16, 8, 8192),
+                          movivik_parallel_shape(2048, 16, 8, 8192, 8), "movivik_parallel"),
+                "w4096": (guvolix_shape(4096, 32, 8, 12288, 4), _qwen3_shape(4096, 4, 32, 8, 12288),
+                          movivik_parallel_shape(4096, 32, 8, 12288, 4), "movivik_parallel")},
 }
 
 
@@ -289,9 +333,10 @@ def _tensors_of(obj, seen=None):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("--design", default="", choices=["", "madevik", "movivik", "bozevik"],
-                    help="madevik, movivik, bozevik: time that design beside the Qwen3 dense shape of equal size (bozevik: also "
-                         "beside a Madevik model of latent-attention layers) instead of the default workload")
+    ap.add_argument("--design", default="", choices=["", "madevik", "movivik", "bozevik", "guvolix"],
+                    help="madevik, movivik, bozevik, guvolix: time that design beside the Qwen3 dense shape of equal size (bozevik: "
+                         "also beside a Madevik model of latent-attention layers; guvolix: also beside a Movivik model of "
+                         "parallel layers) instead of the default workload")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of the sizes of --design, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

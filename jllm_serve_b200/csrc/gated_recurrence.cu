@@ -16,7 +16,7 @@
 //   ssm_gates     dt = softplus(dt_raw + dt_bias); la = -exp(A_log) dt; b = dt                        per (row, head)
 //   memory_gates  i = cap tanh((i_raw + bi) / cap), f = logsigmoid(cap tanh((f_raw + bf) / cap)); m_t = max(f + m_(t-1), i);
 //                 la = f + m_(t-1) - m_t, b = exp(i - m_t), floor = exp(-m_t); m is a state [slots, heads] that starts at 0.
-//                 One thread walks a (segment, head)'s tokens in order: the maximum is a chain.
+//                 The maximum is a chain whose steps compose, so a block shares a (segment, head)'s tokens out in runs.
 // and the short causal convolution per channel in front of the state space:
 //   causal_conv   y[t, c] = silu(bias[c] + sum_r w[c, r] u[t - (taps - 1) + r, c]), u from the rows of the same segment, and
 //                 in front of the segment's first row from the request's state [slots, taps - 1, channels] (float32: the raw
@@ -43,30 +43,93 @@ __global__ void ssm_gates_kernel(const float* __restrict__ dt_raw, int ld, VecRe
     b[i] = dt;
 }
 
-__global__ void memory_gates_kernel(const float* __restrict__ raw, int ld, int i_off, int f_off, VecRef i_bias, VecRef f_bias,
-                                    float cap, float* __restrict__ mstate, int num_slots, const int* __restrict__ seg_start,
-                                    const int* __restrict__ seg_len, const int* __restrict__ state_slots, float* __restrict__ la,
-                                    float* __restrict__ b, float* __restrict__ floor_out, int segments, int heads) {
+// A block per (segment, head). The running maximum m_t = max(f_t + m_(t-1), i_t) is a chain, but one whose steps compose: a
+// run of tokens acts on the m in front of it as m -> max(m + F, I) with F the sum of its f and I what the run alone would
+// leave; two runs in a row give (F1 + F2, max(I1 + F2, I2)). Every thread takes a run of neighbouring tokens (the gates'
+// transcendental functions are the work, and they are all independent), the runs' maps are composed in order by one thread,
+// and every thread walks its run again from the m that stands in front of it.
+__global__ void __launch_bounds__(256)
+memory_gates_kernel(const float* __restrict__ raw, int ld, int i_off, int f_off, VecRef i_bias, VecRef f_bias,
+                    float cap, float* __restrict__ mstate, int num_slots, const int* __restrict__ seg_start,
+                    const int* __restrict__ seg_len, const int* __restrict__ state_slots, float* __restrict__ la,
+                    float* __restrict__ b, float* __restrict__ floor_out, int segments, int heads) {
+    __shared__ float sF[256], sI[256];
     pdl_wait();
     pdl_trigger();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= segments * heads) return;
-    const int seg = i / heads, h = i - seg * heads;
+    const int seg = blockIdx.x / heads, h = blockIdx.x - seg * heads, tid = threadIdx.x;
     const int first = seg_start[seg], n = seg_len[seg], slot = state_slots[seg];
     if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
-    float m = mstate[(size_t)slot * heads + h];
     const float bi = i_bias[h], bf = f_bias[h], inv_cap = 1.f / cap;
-    for (int t = 0; t < n; ++t) {
+    const int per = (n + 255) / 256, lo = min(n, tid * per), hi = min(n, lo + per);
+    auto gates = [&](int t, float& ig, float& fg) {
         const size_t r = (size_t)(first + t);
-        const float ig = cap * tanhf((raw[r * ld + i_off + h] + bi) * inv_cap);
-        const float fg = logsigmoid_f(cap * tanhf((raw[r * ld + f_off + h] + bf) * inv_cap));
+        ig = cap * tanhf((raw[r * ld + i_off + h] + bi) * inv_cap);
+        fg = logsigmoid_f(cap * tanhf((raw[r * ld + f_off + h] + bf) * inv_cap));
+    };
+    // this thread's run as a map of the m in front of it: (F, I); an empty run is (0, -inf)
+    float F = 0.f, I = -INFINITY;
+    for (int t = lo; t < hi; ++t) {
+        float ig, fg;
+        gates(t, ig, fg);
+        F += fg;
+        I = fmaxf(I + fg, ig);
+    }
+    sF[tid] = F;
+    sI[tid] = I;
+    __syncthreads();
+    // the m in front of every run: thread 0 walks the 256 maps in order (each step an add and a max)
+    if (tid == 0) {
+        float m = mstate[(size_t)slot * heads + h];
+        for (int k = 0; k < 256; ++k) {
+            const float f_run = sF[k], i_run = sI[k];
+            sF[k] = m;
+            m = fmaxf(m + f_run, i_run);
+        }
+        mstate[(size_t)slot * heads + h] = m;
+    }
+    __syncthreads();
+    float m = sF[tid];
+    for (int t = lo; t < hi; ++t) {
+        float ig, fg;
+        gates(t, ig, fg);
         const float m_new = fmaxf(fg + m, ig);
+        const size_t r = (size_t)(first + t);
         la[r * heads + h] = fg + m - m_new;
         b[r * heads + h] = expf(ig - m_new);
         floor_out[r * heads + h] = expf(-m_new);
         m = m_new;
     }
-    mstate[(size_t)slot * heads + h] = m;
+}
+
+// The normalizer of a matrix memory as one more value column. n_t = a_t n_(t-1) + b_t k_t is the recurrence of S with a value
+// that is always 1, and n_t . q is that column's output: so the values get a column of ones behind them (`memory_values`: a
+// head's dv values, a 1, zeros up to a width of dvp), the state is [dk, dvp] with n in column dv, the recurrence (token by
+// token or in chunks) needs no case of its own, and `memory_divide` takes the column out again:
+// o[:, :dv] / (max(|o[:, dv]|, floor) + 1e-6).
+template <typename T>
+__global__ void __launch_bounds__(256)
+memory_values_kernel(const T* __restrict__ v, int ld, int off, T* __restrict__ out, int heads, int dv, int dvp) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y, width = heads * dvp;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
+        const int h = i / dvp, c = i - h * dvp;
+        out[(size_t)r * width + i] = c < dv ? v[(size_t)r * ld + off + (size_t)h * dv + c] : from_float<T>(c == dv ? 1.f : 0.f);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+memory_divide_kernel(const float* __restrict__ o, const float* __restrict__ floor_in, float* __restrict__ out, int heads, int dv,
+                     int dvp) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y, width = heads * dv;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
+        const int h = i / dv, c = i - h * dv;
+        const float* src = o + ((size_t)r * heads + h) * dvp;
+        const float den = fmaxf(fabsf(src[dv]), floor_in[(size_t)r * heads + h]) + 1e-6f;
+        out[(size_t)r * width + i] = src[c] / den;
+    }
 }
 
 // ---- the short convolution -------------------------------------------------------------------------------------------
@@ -85,15 +148,14 @@ causal_conv_kernel(const TI* __restrict__ u, int ld, int off, VecRef w, VecRef b
     if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
     float* st = state + (size_t)slot * (taps - 1) * channels;
     float acc = bias[c];
-    float in[MAX_TAPS];
     for (int j = 0; j < taps; ++j) {            // tap j reads the input of local index t - (taps - 1) + j
         const int at = t - (taps - 1) + j;
-        in[j] = at >= 0 ? to_float(u[(size_t)(r - (taps - 1) + j) * ld + off + c]) : st[(size_t)(taps - 1 + at) * channels + c];
+        const float in = at >= 0 ? to_float(u[(size_t)(r - (taps - 1) + j) * ld + off + c]) : st[(size_t)(taps - 1 + at) * channels + c];
+        acc = fmaf(w[(size_t)c * taps + j], in, acc);
+        // a step of single rows (t = 0): this thread alone touches (slot, channel); entry j - 1 has been read one turn ago
+        if (single && j > 0) st[(size_t)(j - 1) * channels + c] = in;
     }
-    for (int j = 0; j < taps; ++j) acc = fmaf(w[(size_t)c * taps + j], in[j], acc);
     y[(size_t)r * ld_y + c] = from_float<TO>(acc / (1.f + expf(-acc)));
-    if (single)                                 // a step of single rows: this thread alone touches (slot, channel)
-        for (int j = 0; j + 1 < taps; ++j) st[(size_t)j * channels + c] = in[j + 1];
 }
 
 template <typename TI>
@@ -297,10 +359,38 @@ JLLM_EXPORT int jllm_memory_gates(const float* raw, int ld, int i_off, int f_off
                  (double)cap);
     if (segments == 0) return JLLM_OK;
     const int total = segments * heads;
-    jllm_launch(memory_gates_kernel, dim3((total + 63) / 64), dim3(64), 0, stream, LAUNCH_DEPENDENT, raw, ld, i_off, f_off,
+    jllm_launch(memory_gates_kernel, dim3(total), dim3(256), 0, stream, LAUNCH_DEPENDENT, raw, ld, i_off, f_off,
                 VecRef{i_bias, vec_dtype}, VecRef{f_bias, vec_dtype}, cap, mstate, num_slots, seg_start, seg_len, state_slots,
                 la, b, floor_out, segments, heads);
     return jllm_check_launch("memory_gates");
+}
+
+// v: a view [rows, ld] of type `dtype` with heads x dv values at column `off`; out [rows, heads x dvp] of the same type.
+JLLM_EXPORT int jllm_memory_values(const void* v, int dtype, int ld, int off, void* out, int rows, int heads, int dv, int dvp,
+                                   cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && rows <= 65535 && heads > 0 && dv > 0 && dvp > dv, "memory_values: rows=%d heads=%d dv=%d dvp=%d", rows,
+                 heads, dv, dvp);
+    if (rows == 0) return JLLM_OK;
+    const dim3 grid(max(1, min(32, (heads * dvp + 255) / 256)), rows);
+    if (dtype == JLLM_F32)
+        jllm_launch(memory_values_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)v, ld, off, (float*)out,
+                    heads, dv, dvp);
+    else
+        jllm_launch(memory_values_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)v, ld,
+                    off, (__nv_bfloat16*)out, heads, dv, dvp);
+    return jllm_check_launch("memory_values");
+}
+
+// o [rows, heads x dvp] float32 with the normalizer's output in column dv of every head; floor_in [rows, heads]; out
+// [rows, heads x dv] float32.
+JLLM_EXPORT int jllm_memory_divide(const float* o, const float* floor_in, float* out, int rows, int heads, int dv, int dvp,
+                                   cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && rows <= 65535 && heads > 0 && dv > 0 && dvp > dv, "memory_divide: rows=%d heads=%d dv=%d dvp=%d", rows,
+                 heads, dv, dvp);
+    if (rows == 0) return JLLM_OK;
+    const dim3 grid(max(1, min(32, (heads * dv + 255) / 256)), rows);
+    jllm_launch(memory_divide_kernel, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o, floor_in, out, heads, dv, dvp);
+    return jllm_check_launch("memory_divide");
 }
 
 // u: a view [rows, ld] of type `in_dtype` whose columns [off, off + channels) are the convolution's inputs; w [channels, taps]

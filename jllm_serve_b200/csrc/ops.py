@@ -187,6 +187,8 @@ class _Signatures:
     jllm_causal_conv = [P, I, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_scalar_gated_recurrent = [P, I, I, I, P, I, I, I, P, I, I, I, P, P, P, P, I, P, P, I, P, P, P, P, I, I, I, I, F, P]
     jllm_scalar_gated_chunked = [P, I, I, I, P, I, I, I, P, I, I, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, P]
+    jllm_memory_values = [P, I, I, I, P, I, I, I, I, P]
+    jllm_memory_divide = [P, P, P, I, I, I, I, P]
     jllm_sigmoid_gate = [P, I, P, I, I, I, I, F, P]
     jllm_activation = [P, I, ctypes.c_longlong, I, P]
     jllm_add_rows_scaled = [P, P, I, I, P, I, I, I, P]
@@ -509,6 +511,21 @@ def scalar_gated_recurrent(q, q_off, q_groups, k, k_off, k_groups, v, v_off, log
           in_scale.data_ptr(), _p(floor), _p(skip), _DT[skip.dtype] if skip is not None else F32, state.data_ptr(),
           _p(normalizer), state.shape[0], batch.seg_start.data_ptr(), batch.seg_len.data_ptr(), batch.state_slots.data_ptr(),
           out.data_ptr(), batch.seg_start.numel(), int(heads), int(key_dim), int(value_dim), float(query_scale), _stream())
+
+
+def memory_values(v, off, heads, value_dim, padded, out) -> None:
+    """out[r, h] = [v[r, h, :value_dim], 1, 0, ...] (padded values a head): the values of a matrix memory with the column of
+    ones behind them that carries its normalizer through the recurrence. v a view [rows, *], out [rows, heads x padded]."""
+    assert v.dtype == out.dtype and v.stride(1) == 1 and out.is_contiguous() and out.shape[1] == heads * padded
+    _call("jllm_memory_values", v.data_ptr(), _DT[v.dtype], v.stride(0), int(off), out.data_ptr(), v.shape[0], int(heads),
+          int(value_dim), int(padded), _stream())
+
+
+def memory_divide(o, floor, out, heads, value_dim, padded) -> None:
+    """out[r, h, :] = o[r, h, :value_dim] / (max(|o[r, h, value_dim]|, floor[r, h]) + 1e-6); all float32 and contiguous."""
+    assert o.dtype == floor.dtype == out.dtype == torch.float32 and o.is_contiguous() and floor.is_contiguous() and out.is_contiguous()
+    _call("jllm_memory_divide", o.data_ptr(), floor.data_ptr(), out.data_ptr(), o.shape[0], int(heads), int(value_dim), int(padded),
+          _stream())
 
 
 GATED_CHUNKS = int(os.environ.get("JLLM_B200_GATED_CHUNKS", "1"))      # 0: prompt portions token by token everywhere

@@ -50,6 +50,10 @@ class GqaAttention(Mixer):
         # the classic form (one head width, pairs (i, i + half), nothing behind the rotation) runs on the fused kernels that
         # were built for it; everything else on the general per-head kernel
         self.classic = (vd == hd and not spec.unit_qk and (rope is None or rope.pairing == "half"))
+        if self.classic and spec.gate == "sigmoid" and rope is not None and rope.rotary_dim != hd and hd in (64, 128, 256):
+            # a rotation of part of such a head: the general kernel's register form is the faster one (2,048 rows of 16 + 8
+            # heads of 128: 14 us against 70)
+            self.classic = False
         w = [tensors.pop(prefix + n) for n in (names.q, names.k, names.v)]
         b = [tensors.pop(prefix + n) for n in (names.q_bias, names.k_bias, names.v_bias)] if spec.bias else None
         self.k_off, self.v_off = self.q_width, self.q_width + self.k_width

@@ -85,7 +85,7 @@ def test_what_the_runs_keep_between_steps():
             self._block_states = [0] * len(spec.schedule)
     needs = Shell(spec).cache_needs()
     assert needs[0] == (PagedKeysValues(2, 24, 20, keep_first=5), FixedState((6, 12, 8)), FixedState((2, 120)))
-    assert needs[1] == (PagedKeysValues(3, 24, 13), FixedState((3, 12, 20)), FixedState((3, 12)), FixedState((3,)))
+    assert needs[1] == (PagedKeysValues(3, 24, 13), FixedState((3, 12, 24)), FixedState((3,)))      # (20 values, the normalizer, zeros)
     one_tap = Shell(parse_config(GUVOLIX["C"])).cache_needs()[1]
     assert one_tap[2] == FixedState((1, 3 * 24 + 2 * 3 * 16))
 
