@@ -1318,7 +1318,9 @@ JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype
     const VecRef g{gain, gain_dtype};
     const long long warps = (long long)rows * heads;
     const bool wide_gate = gate_dtype != dtype;
-    if (dv > 512 && warps <= 2147483647ll) {       // long norms: a block each
+    // long norms: a block each; also norms of 256 values and more where a step has so few of them that a warp each would
+    // leave the device idle (a step of single rows)
+    if ((dv > 512 || (dv >= 256 && warps <= 2048)) && warps <= 2147483647ll) {
         if (dtype == JLLM_F32)
             jllm_launch(gated_row_norm_kernel<float>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
                         (const float*)gate, ld_gate, g, (float*)y, heads, dv, eps, scale, gate_kind);

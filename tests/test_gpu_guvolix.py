@@ -230,7 +230,7 @@ def test_the_sink_counts_once_and_is_not_scaled():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("channels, taps", [(37, 4), (576, 4), (64, 2), (20, 1), (130, 7)])
+@pytest.mark.parametrize("channels, taps", [(37, 4), (520, 4), (64, 2), (20, 1), (130, 7)])
 def test_causal_convolution_over_segments_slots_and_portions(dtype, channels, taps):
     """A request's rows in three steps (a portion, another, then single rows) give what the whole sequence gives; the state
     of a slot that another request used before is what that request left, and a fresh one is zero."""
@@ -449,7 +449,7 @@ def test_gate_in_front_of_a_norm_in_parts_and_a_gain_per_column(dtype, groups, w
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts, identity, top, gates", [(12, 2, 4, 1), (3, 0, 1, 0), (5, 3, 8, 1), (4, 1, 2, 0), (2, 2, 1, 1)])
+@pytest.mark.parametrize("experts, identity, top, gates", [(10, 3, 4, 1), (3, 0, 1, 0), (5, 3, 8, 1), (4, 1, 2, 0), (2, 2, 1, 1)])
 def test_the_router_with_softmax_scores_identity_entries_and_a_gate(dtype, experts, identity, top, gates):
     o = ops()
     g = torch.Generator().manual_seed(experts * 10 + top)
