@@ -158,6 +158,47 @@ causal_conv_kernel(const TI* __restrict__ u, int ld, int off, VecRef w, VecRef b
     y[(size_t)r * ld_y + c] = from_float<TO>(acc / (1.f + expf(-acc)));
 }
 
+// The same for prompt portions with a window of inputs in registers: a thread owns one channel of ROWS neighbouring rows, so
+// an input is read once and not `taps` times. Where a row begins a segment (or the thread's run) the window is filled anew, from
+// the rows in front of it or, in front of the segment's first row, from the request's state.
+template <typename TI, typename TO, int TAPS, int ROWS>
+__global__ void __launch_bounds__(256)
+causal_conv_rows_kernel(const TI* __restrict__ u, int ld, int off, VecRef w, VecRef bias, const float* __restrict__ state,
+                        int num_slots, const int* __restrict__ row_seg, const int* __restrict__ seg_start,
+                        const int* __restrict__ state_slots, TO* __restrict__ y, int ld_y, int rows, int channels) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r0 = blockIdx.y * ROWS;
+    if (c >= channels) return;
+    float wt[TAPS], win[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j];
+    const float bc = bias[c];
+    int seg_now = -1;
+    for (int r = r0; r < min(rows, r0 + ROWS); ++r) {
+        const int seg = row_seg[r];
+        const float in = to_float(u[(size_t)r * ld + off + c]);
+        if (seg != seg_now) {           // the window in front of this row: earlier rows of the segment, else the state
+            seg_now = seg;
+            const int t = r - seg_start[seg], slot = state_slots[seg];
+            const bool ok = jllm_in_bounds(slot, num_slots, BOUNDS_SLOT);
+            const float* st = state + (size_t)(ok ? slot : 0) * (TAPS - 1) * channels;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int at = t - (TAPS - 1) + j;
+                win[j] = at >= 0 ? to_float(u[(size_t)(r - (TAPS - 1) + j) * ld + off + c]) : (ok ? st[(size_t)(TAPS - 1 + at) * channels + c] : 0.f);
+            }
+        }
+        win[TAPS - 1] = in;
+        float acc = bc;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) acc = fmaf(wt[j], win[j], acc);
+        y[(size_t)r * ld_y + c] = from_float<TO>(acc / (1.f + expf(-acc)));
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS; ++j) win[j] = win[j + 1];
+    }
+}
+
 template <typename TI>
 __global__ void __launch_bounds__(256)
 conv_state_kernel(const TI* __restrict__ u, int ld, int off, float* __restrict__ state, int num_slots,
@@ -405,8 +446,17 @@ JLLM_EXPORT int jllm_causal_conv(const void* u, int in_dtype, int ld, int off, c
     JLLM_REQUIRE(rows <= 65535 && segments <= 65535, "causal_conv: %d rows or %d segments in one launch", rows, segments);
     const VecRef wv{w, vec_dtype}, bv{bias, vec_dtype};
     const dim3 grid((channels + 255) / 256, rows), sgrid((channels + 255) / 256, segments);
+    constexpr int RUN = 16;      // rows of a thread's run in the windowed form
+    const dim3 rgrid((channels + 255) / 256, (rows + RUN - 1) / RUN);
+#define JLLM_CONV_ROWS(TI, TO, TAPS)                                                                                            \
+    jllm_launch(causal_conv_rows_kernel<TI, TO, TAPS, RUN>, rgrid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const TI*)u, ld,    \
+                off, wv, bv, (const float*)state, num_slots, row_seg, seg_start, state_slots, (TO*)y, ld_y, rows, channels)
 #define JLLM_CONV(TI, TO)                                                                                                       \
     do {                                                                                                                        \
+        if (!single && taps == 4) JLLM_CONV_ROWS(TI, TO, 4);                                                                    \
+        else if (!single && taps == 3) JLLM_CONV_ROWS(TI, TO, 3);                                                               \
+        else if (!single && taps == 2) JLLM_CONV_ROWS(TI, TO, 2);                                                               \
+        else                                                                                                                    \
         jllm_launch(causal_conv_kernel<TI, TO>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const TI*)u, ld, off, wv, bv,    \
                     state, num_slots, row_seg, seg_start, state_slots, (TO*)y, ld_y, rows, channels, taps, single);             \
         if (!single && taps > 1)                                                                                                \
@@ -418,6 +468,7 @@ JLLM_EXPORT int jllm_causal_conv(const void* u, int in_dtype, int ld, int off, c
     else if (out_dtype == JLLM_F32) JLLM_CONV(__nv_bfloat16, float);
     else JLLM_CONV(__nv_bfloat16, __nv_bfloat16);
 #undef JLLM_CONV
+#undef JLLM_CONV_ROWS
     return jllm_check_launch("causal_conv");
 }
 
