@@ -315,8 +315,7 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
                  int kv_heads, int head_dim, int page_size, int window, float scale, int splits, float* scratch,
                  const staged::Fresh& fresh, cudaStream_t stream, int keep_first = 0, const void* sink = nullptr,
                  int sink_dtype = JLLM_F32) {
-    // (kept first keys and a sink are the general kernel's: the staged kernels stream whole runs of neighbouring keys)
-    const bool extras = keep_first > 0 || sink != nullptr;
+    // (kept first keys and a sink: the staged kernels of one block per (row, kv head, split) and the general kernel take them)
     const VecRef sk{sink, sink_dtype};
     const int has_sink = sink != nullptr;
     JLLM_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_decode: keep_first=%d needs a window", keep_first);
@@ -337,7 +336,7 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
     float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
     const float scale_log2 = scale * LOG2E;
     const int hdc = (head_dim + 63) / 64;
-    if (!extras && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+    if (head_dim == 64 || head_dim == 128 || head_dim == 256) {
         // the common head sizes stream the cache through a shared-memory ring (attention_decode_staged.cuh)
         // The last block of a (row, kv head) pair adds the pair's partials up itself where the library's counters reach,
         // up to 8 splits: with more (few rows, long ranges) one block's adding of all of a pair's parts is slower than
@@ -346,13 +345,14 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
                             ? staged::pair_counters() : nullptr;
 #define JLLM_STAGED(HD)                                                                                             \
     staged::launch<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, fresh, stream)
+                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, fresh, stream, \
+                       keep_first, sk)
         if (head_dim == 64) JLLM_STAGED(64); else if (head_dim == 128) JLLM_STAGED(128); else JLLM_STAGED(256);
 #undef JLLM_STAGED
         int rc2 = jllm_check_launch("attention_decode_staged");
         if (rc2 != JLLM_OK || splits == 1 || counters != nullptr) return rc2;
         jllm_launch(attention_combine_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
-                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits, VecRef{nullptr, JLLM_F32}, 0);
+                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits, sk, has_sink);
         return jllm_check_launch("attention_combine");
     }
     JLLM_REQUIRE(fresh.qkv == nullptr, "attention_decode: head_dim=%d has no kernel that norms and rotates its own row", head_dim);
@@ -378,7 +378,7 @@ int decode_split(const void* q, int q_stride, const void* k_cache, const void* v
 }  // namespace
 
 // The same with a window that keeps the request's first `keep_first` keys visible and / or a sink per query head (`sink`
-// [heads] of type `sink_dtype`, or null): every head size on the general kernel.
+// [heads] of type `sink_dtype`, or null).
 JLLM_EXPORT int jllm_attention_decode_extras(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                              int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
                                              int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,

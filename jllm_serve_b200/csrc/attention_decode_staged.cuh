@@ -85,6 +85,16 @@ __device__ __forceinline__ void head_store(uint8_t* tile, int row, int lane, con
     }
 }
 
+// What a mixer may add to the attention: the request's first `kept` keys stay visible in front of the window (the caller
+// then passes a `first` that lies `kept` keys EARLIER than the window's first key: the row's visible keys are numbered from
+// there, the first `kept` numbers are the keys 0 .. kept - 1 and every later number is the key itself), and a sink per query
+// head whose exponential joins the sum where a row's keys are all together.
+struct Extras {
+    int kept = 0;
+    VecRef sink{nullptr, JLLM_F32};
+    int has_sink = 0;
+};
+
 // The keys [first + tile_lo * 64, ...) of n_tiles tiles of one (row, kv head), for the G query heads of that kv head:
 // the result goes to `out` if these are all the row's keys (`whole`), else as a partial (sums, maximum, weight) for
 // head j of the group to part_o + j * o_stride and part_ml + j * ml_stride. All threads of the block call it.
@@ -96,7 +106,7 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
                                        float scale_log2, int r, int kvh, int P,
                                        int first, int tile_lo, int n_tiles, bool whole, float* __restrict__ part_o,
                                        size_t o_stride, float* __restrict__ part_ml, size_t ml_stride,
-                                       const Fresh& fresh, bool early = false) {
+                                       const Fresh& fresh, bool early = false, const Extras ex = Extras{}) {
     // `early`: the block has not yet waited for the kernel in front of it (programmatic dependent launch). That kernel
     // wrote the queries and the key and value of position P; the block tables and the positions came from the host
     // before the step, and the keys and values of earlier positions were written by earlier steps. So the rows of
@@ -125,9 +135,10 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     __shared__ __align__(16) __nv_bfloat16 s_fresh[2 * HD];       // the row's newest key and value (a fresh launch)
     auto find_rows = [&](int i) {
         if (i < n_tiles && threadIdx.x < TILE) {
-            const int key = first + (tile_lo + i) * TILE + threadIdx.x;
+            const int number = first + (tile_lo + i) * TILE + threadIdx.x;
             long long o = -1;
-            if (key <= P) {
+            if (number <= P) {
+                const int key = number < first + ex.kept ? number - first : number;      // (the kept keys come first)
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
                 const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
                 const long long page = jllm_page_of(table, pg, table_len, num_pages);   // -1: checked build, bad entry
@@ -363,6 +374,11 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
             ll += mw == -INFINITY ? 0.f : sml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
         }
         if (whole) {
+            if (ex.has_sink) {         // (2^(sink - max) may overflow where every score lies far below the sink: the result is 0)
+                const float sl = ex.sink[kvh * G + row] * LOG2E, top = fmaxf(mm, sl);
+                acc *= exp2f(mm - top);
+                ll = ll * exp2f(mm - top) + exp2f(sl - top);
+            }
             out[(size_t)r * out_stride + (size_t)(kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
         } else {
             part_o[(size_t)row * o_stride + d] = acc;
@@ -404,7 +420,8 @@ __device__ __forceinline__ bool last_of_pair(int* counter, int expected) {
 template <int HD>
 __device__ __forceinline__ void combine_pair(const float* __restrict__ po, size_t o_part, size_t o_row,
                                              const float* __restrict__ pml, size_t ml_part, size_t ml_row, int parts,
-                                             int G, __nv_bfloat16* __restrict__ out_pair) {
+                                             int G, __nv_bfloat16* __restrict__ out_pair, const Extras ex = Extras{},
+                                             int head0 = 0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int row = warp; row < G; row += WARPS) {
         float ms[2], ls[2], w[2];
@@ -417,7 +434,9 @@ __device__ __forceinline__ void combine_pair(const float* __restrict__ po, size_
         float M = fmaxf(ms[0], ms[1]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        float L = 0.f;
+        const float sl = ex.has_sink ? ex.sink[head0 + row] * LOG2E : -INFINITY;      // the sink joins the maximum and the sum once
+        M = fmaxf(M, sl);
+        float L = ex.has_sink ? exp2f(sl - M) : 0.f;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             w[h] = ms[h] == -INFINITY ? 0.f : exp2f(ms[h] - M);
@@ -458,14 +477,18 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                                const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
                                int heads, int kv_heads, int page_size, int num_pages, int window, float scale_log2,
                                int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                               int* __restrict__ counters, const Fresh fresh) {
+                               int* __restrict__ counters, const Fresh fresh, int keep_first, VecRef sink, int has_sink) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = heads / kv_heads;
     // (the wait for the kernel in front, which wrote the newest key and value of every row and the queries, is inside
     // `attend`, behind the look-ups and the first requests that do not depend on it)
     const int P = row_pos[r];
-    const int first = jllm_first_key(P, window);
+    Extras ex;
+    ex.kept = jllm_kept_keys(jllm_first_key(P, window), window, keep_first);
+    ex.sink = sink;
+    ex.has_sink = has_sink;
+    const int first = jllm_first_key(P, window) - ex.kept;      // the row's visible keys are numbered from here
     const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
     const int tiles_per_split = (tiles_total + splits - 1) / splits;
     const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
@@ -474,12 +497,12 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     const size_t slot = ((size_t)r * heads + kvh * G) * splits + split;
     attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, table_stride, num_pages, heads, kv_heads,
                page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD,
-               (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, fresh, true);
+               (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, fresh, true, ex);
     // (without counters a combine kernel follows)
     if (splits > 1 && counters != nullptr && last_of_pair(counters + (size_t)r * kv_heads + kvh, splits)) {
         const size_t slot0 = ((size_t)r * heads + kvh * G) * splits;
         combine_pair<HD>(part_o + slot0 * HD, (size_t)HD, (size_t)splits * HD, part_ml + slot0 * 2, (size_t)2,
-                         (size_t)splits * 2, splits, G, out + (size_t)r * out_stride + (size_t)kvh * G * HD);
+                         (size_t)splits * 2, splits, G, out + (size_t)r * out_stride + (size_t)kvh * G * HD, ex, kvh * G);
     }
 }
 
@@ -644,7 +667,7 @@ template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
             int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
-            int* counters, const Fresh& fresh, cudaStream_t stream) {
+            int* counters, const Fresh& fresh, cudaStream_t stream, int keep_first = 0, VecRef sink = VecRef{nullptr, JLLM_F32}) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -653,7 +676,8 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml, counters, fresh);
+        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml, counters, fresh, keep_first, sink,
+        (int)(sink.p != nullptr));
 }
 
 // The library's pair counters on the current device (nullptr: the combine kernels run instead).
