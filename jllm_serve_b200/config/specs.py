@@ -220,6 +220,8 @@ class SelectiveStateSpaceSpec(MixerSpec):
             raise ConfigError(f"state space: norm_groups={self.norm_groups} must divide heads x vdim={self.heads * self.head_dim}")
         if self.conv > 16:
             raise ConfigError(f"state space: conv={self.conv} taps (built: up to 16)")
+        if self.state > 1024:
+            raise ConfigError(f"state space: state={self.state} (built: up to 1024)")
 
     @property
     def inner(self) -> int:
@@ -250,8 +252,8 @@ class MatrixMemorySpec(MixerSpec):
                 raise ConfigError(f"matrix memory: {name}={getattr(self, name)} must be positive")
         if not self.gate_cap > 0:
             raise ConfigError(f"matrix memory: gate_cap={self.gate_cap} must be positive")
-        if self.key_dim > 512:
-            raise ConfigError(f"matrix memory: dim={self.key_dim} (built: up to 512)")
+        if self.key_dim > 1024:
+            raise ConfigError(f"matrix memory: dim={self.key_dim} (built: up to 1024)")
 
 
 @dataclass(frozen=True)

@@ -481,8 +481,9 @@ JLLM_EXPORT int jllm_scalar_gated_recurrent(const void* q, int ld_q, int q_off, 
                                             float* state, float* nstate, int num_slots, const int* seg_start,
                                             const int* seg_len, const int* state_slots, float* o, int segments, int heads,
                                             int dk, int dv, float q_scale, cudaStream_t stream) {
-    JLLM_REQUIRE(segments >= 0 && heads > 0 && dk > 0 && dk <= 512 && dv > 0, "scalar_gated_recurrent: segments=%d heads=%d dk=%d "
-                 "(at most 512) dv=%d", segments, heads, dk, dv);
+    JLLM_REQUIRE(segments >= 0 && heads > 0 && dk > 0 && dk <= 1024 && (nstate == nullptr || dk <= 512) && dv > 0,
+                 "scalar_gated_recurrent: segments=%d heads=%d dk=%d (at most 1024; 512 with a normalizer) dv=%d", segments, heads,
+                 dk, dv);
     JLLM_REQUIRE(q_groups > 0 && k_groups > 0 && heads % q_groups == 0 && heads % k_groups == 0,
                  "scalar_gated_recurrent: %d heads do not share %d queries or %d keys evenly", heads, q_groups, k_groups);
     JLLM_REQUIRE(nstate == nullptr || floor_in != nullptr, "scalar_gated_recurrent: a normalizer needs its floor");

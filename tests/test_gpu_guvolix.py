@@ -324,7 +324,8 @@ def plain_recurrence(q, k, v, la, b, S, n=None, floor=None, skip=None, q_scale=1
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H, G, dk, dv, form", [(6, 3, 12, 8, "space"), (2, 1, 48, 40, "space"), (4, 4, 64, 64, "space"), (3, 3, 5, 7, "memory"),
-                                                (2, 2, 128, 72, "memory"), (1, 1, 300, 33, "memory"), (8, 2, 16, 130, "space")])
+                                                (2, 2, 128, 72, "memory"), (1, 1, 300, 33, "memory"), (8, 2, 16, 130, "space"),
+                                                (2, 1, 700, 20, "space")])
 def test_the_recurrence_over_segments_slots_and_portions(dtype, H, G, dk, dv, form):
     """Two requests in three steps (portions, then single rows), their states in slots that are not in request order; keys
     and queries shared by the heads of a group (state space) or a head's own with a normalizer and its floor (memory)."""
