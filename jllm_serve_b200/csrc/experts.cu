@@ -69,7 +69,9 @@ route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ 
         }
     }
     __syncthreads();
-    float* out = weights + (size_t)r * ld_out;
+    // the row's table is put together in shared memory (one thread's choice is a chain of dependent steps: in global memory
+    // every step of it was a round trip) and written out by all threads
+    float* out = hs + ((dim + 3) & ~3);
     for (int e = threadIdx.x; e < ld_out; e += blockDim.x) out[e] = 0.f;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -101,6 +103,9 @@ route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ 
         for (int g = 0; g < gates; ++g) out[real + g] = __fmul_rn(s[entries + g], scale);
         if (identity) out[real + gates] = __fmul_rn(through, f);
     }
+    __syncthreads();
+    float* dst = weights + (size_t)r * ld_out;
+    for (int e = threadIdx.x; e < ld_out; e += blockDim.x) dst[e] = out[e];
 }
 
 template <typename T>
@@ -246,7 +251,7 @@ JLLM_EXPORT int jllm_route_experts(const void* h, int dtype, int ld, const float
     if (rows == 0) return JLLM_OK;
     const VecRef c{correction, correction_dtype};
     const int padded = (experts + 1) / 2 * 2;       // the row's copy behind the two score arrays starts on 16 bytes
-    const size_t smem = (2 * (size_t)padded + dim) * sizeof(float);
+    const size_t smem = (2 * (size_t)padded + ((dim + 3) & ~3) + ld_out) * sizeof(float);
     JLLM_REQUIRE(smem <= 200 * 1024, "route_experts: dim=%d and experts=%d need %zu bytes of shared memory", dim, experts, smem);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(route_experts_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||

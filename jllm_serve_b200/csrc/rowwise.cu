@@ -853,10 +853,71 @@ norm_sum_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain_
     }
 }
 
+// The same with the rows in registers between the sums and the results: a thread owns V groups of four neighbouring values
+// of each row (dim a multiple of 4, at most 256 x 4 V values), every row is read once and all of a thread's loads are on their
+// way together. The same arithmetic in the same order per value; the sums of squares are grouped by thread, as above.
+template <int V>
+__global__ void __launch_bounds__(256)
+norm_sum_vec_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain_a, const float* __restrict__ b, VecRef gain_b,
+                    int dim, float eps, float scale, int accumulate) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t row = (size_t)blockIdx.x * dim;
+    const int groups = dim >> 2;
+    float4 va[V], vb[V];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+        const int gi = threadIdx.x + u * 256;
+        va[u] = gi < groups ? *reinterpret_cast<const float4*>(a + row + 4 * gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+        vb[u] = (b && gi < groups) ? *reinterpret_cast<const float4*>(b + row + 4 * gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+        sa = fmaf(va[u].x, va[u].x, sa); sa = fmaf(va[u].y, va[u].y, sa); sa = fmaf(va[u].z, va[u].z, sa); sa = fmaf(va[u].w, va[u].w, sa);
+        sb = fmaf(vb[u].x, vb[u].x, sb); sb = fmaf(vb[u].y, vb[u].y, sb); sb = fmaf(vb[u].z, vb[u].z, sb); sb = fmaf(vb[u].w, vb[u].w, sb);
+    }
+    sa = block_sum(sa, scratch);
+    const float ra = rms_scale(sa, dim, eps);
+    float rb = 0.f;
+    if (b) {
+        sb = block_sum(sb, scratch);
+        rb = rms_scale(sb, dim, eps);
+    }
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+        const int gi = threadIdx.x + u * 256;
+        if (gi >= groups) continue;
+        const float pa[4] = {va[u].x, va[u].y, va[u].z, va[u].w}, pb[4] = {vb[u].x, vb[u].y, vb[u].z, vb[u].w};
+        float4 old = accumulate ? *reinterpret_cast<const float4*>(x + row + 4 * gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float res[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = 4 * gi + k;
+            float v = __fmul_rn(__fmul_rn(pa[k], ra), gain_a[i]);
+            if (b) v = __fadd_rn(v, __fmul_rn(__fmul_rn(pb[k], rb), gain_b[i]));
+            v = __fmul_rn(v, scale);
+            res[k] = accumulate ? __fadd_rn(res[k], v) : v;
+        }
+        *reinterpret_cast<float4*>(x + row + 4 * gi) = make_float4(res[0], res[1], res[2], res[3]);
+    }
+}
+
 JLLM_EXPORT int jllm_norm_sum(float* x, const float* a, const void* gain_a, const float* b, const void* gain_b, int gain_dtype,
                               int rows, int dim, float eps, float scale, int accumulate, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && dim > 0 && a && gain_a && (!b || gain_b), "norm_sum: rows=%d dim=%d", rows, dim);
     if (rows == 0) return JLLM_OK;
+    const bool aligned = dim % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 && (!b || ((uintptr_t)b % 16) == 0);
+    if (aligned && dim <= 8192) {
+        const int v = (dim / 4 + 255) / 256;
+#define JLLM_NORM_SUM(V)                                                                                                   \
+    jllm_launch(norm_sum_vec_kernel<V>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, VecRef{gain_a, gain_dtype}, b, \
+                VecRef{gain_b, gain_dtype}, dim, eps, scale, accumulate)
+        if (v <= 1) JLLM_NORM_SUM(1); else if (v <= 2) JLLM_NORM_SUM(2); else if (v <= 4) JLLM_NORM_SUM(4); else JLLM_NORM_SUM(8);
+#undef JLLM_NORM_SUM
+        return jllm_check_launch("norm_sum");
+    }
     jllm_launch(norm_sum_kernel, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, VecRef{gain_a, gain_dtype}, b,
                 VecRef{gain_b, gain_dtype}, dim, eps, scale, accumulate);
     return jllm_check_launch("norm_sum");
